@@ -36,8 +36,10 @@ def registered_architectures():
 
 def resolve_architecture(raw: Dict[str, Any]) -> str:
     """The registered name that a ``config.json`` asks for: the first known entry of
-    ``architectures``, else ``model_type``."""
-    names = raw.get("architectures") or []
+    ``architectures`` (or the one name under ``architecture``), else ``model_type``."""
+    names = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):      # some families name one, in the singular
+        names.append(raw["architecture"])
     for n in names:
         if n in _ARCHITECTURES:
             return n

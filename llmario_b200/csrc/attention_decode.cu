@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(32, 6) flash_decode_kernel(
   const int g = lane >> 2, t = lane & 3;
   const int pairs = it.tokens * G;                 // <= 8
   const int hi = it.pos_start + it.tokens - 1;
-  const int lo = (window > 0 && it.pos_start + 1 > window) ? it.pos_start + 1 - window : 0;
+  const int lo = first_key(it.pos_start, window);
   const int tile_first = lo / KT, tile_last = hi / KT;
   const int ntiles = tile_last - tile_first + 1;
   const int per = (ntiles + splits - 1) / splits;
@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(32, 6) flash_decode_kernel(
     cvalid[j] = n < pairs;
     const int tok = cvalid[j] ? n / G : 0, head = kvh * G + (cvalid[j] ? n % G : 0);
     cpos[j] = it.pos_start + tok;
-    clo[j] = (window > 0 && cpos[j] + 1 > window) ? cpos[j] + 1 - window : 0;
+    clo[j] = first_key(cpos[j], window);
     crow[j] = (size_t)(it.row_start + tok) * Hq + head;
   }
   // Q^T as the B operand: this thread supplies pair n = g

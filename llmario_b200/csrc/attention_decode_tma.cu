@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(32, 4) flash_decode_tma_kernel(
   const int G = Hq / Hkv;
   const int pairs = it.tokens * G;                 // <= 8
   const int hi = it.pos_start + it.tokens - 1;
-  const int lo = (window > 0 && it.pos_start + 1 > window) ? it.pos_start + 1 - window : 0;
+  const int lo = first_key(it.pos_start, window);
   const int tile_first = lo / KT, tile_last = hi / KT;
   const int ntiles = tile_last - tile_first + 1;
   const int per = (ntiles + splits - 1) / splits;
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(32, 4) flash_decode_tma_kernel(
     cvalid[j] = n < pairs;
     const int tok = cvalid[j] ? n / G : 0, head = kvh * G + (cvalid[j] ? n % G : 0);
     cpos[j] = it.pos_start + tok;
-    clo[j] = (window > 0 && cpos[j] + 1 > window) ? cpos[j] + 1 - window : 0;
+    clo[j] = first_key(cpos[j], window);
     crow[j] = (size_t)(it.row_start + tok) * Hq + head;
   }
   uint32_t qf[KS][2];
@@ -484,7 +484,7 @@ __global__ void __launch_bounds__(32, 4) flash_decode_persistent_kernel(
     int tiles = 0;
     if (r < rows) {
       const int pos = row_pos[r];
-      const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+      const int lo = first_key(pos, window);
       tiles = pos / KT - lo / KT + 1;
       s_pos[r] = pos;
       s_slot[r] = row_slot[r];
@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(32, 4) flash_decode_persistent_kernel(
   auto row_info = [&](int r, Cursor& c) {
     c.r = r;
     c.hi = s_pos[r];
-    c.lo = (window > 0 && c.hi + 1 > window) ? c.hi + 1 - window : 0;
+    c.lo = first_key(c.hi, window);
     c.first = c.lo / KT;
     c.t = c.hi / KT - c.first + 1;
     c.slot = s_slot[r];
@@ -844,7 +844,7 @@ LLM_EXPORT int llm_attention_decode_persistent(const void* q, float* part_o, flo
                                                int Hkv, int hd, int page_size, float scale, int window,
                                                int parts, int ctas, int* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (!row_slot || !row_pos || parts < 2 || parts > 32 || ctas <= 0 || window < 0) return LLM_ERR_ARGUMENT;
+  if (!row_slot || !row_pos || parts < 2 || parts > 32 || ctas <= 0) return LLM_ERR_ARGUMENT;
   if (rows > PERSIST_MAX_ROWS || (Hkv > 0 && Hq / Hkv > 8)) return LLM_ERR_UNSUPPORTED;
   CUtensorMap map;
   if (int e = check_and_map(storage, n_pages, n_slots, slot, Hq, Hkv, hd, page_size, parts, part_o, part_ml, &map))

@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 6) flash_paged_ke
   const int g = lane >> 2, t = lane & 3;
   const int rows_valid = it.tokens * G;
   const int hi = it.pos_start + it.tokens - 1;
-  const int lo = (window > 0 && it.pos_start + 1 > window) ? it.pos_start + 1 - window : 0;
+  const int lo = first_key(it.pos_start, window);
   const int tile_first = lo / KT, tile_last = hi / KT;
   const int ntiles = tile_last - tile_first + 1;
   const int per = (ntiles + splits - 1) / splits;
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 6) flash_paged_ke
     rtok[i] = rvalid[i] ? r / G : 0;
     rhead[i] = kvh * G + (rvalid[i] ? r % G : 0);
     rpos[i] = it.pos_start + rtok[i];
-    rlo[i] = (window > 0 && rpos[i] + 1 > window) ? rpos[i] + 1 - window : 0;
+    rlo[i] = first_key(rpos[i], window);
   }
 
   // Q fragments, kept for the whole kernel
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 6) flash_paged_ke
       const int wr0 = warp * 16, wr1 = min(rows_valid, wr0 + 16) - 1;
       const int min_pos = it.pos_start + wr0 / G, max_pos = it.pos_start + wr1 / G;
       const bool interior = base + KT - 1 <= min_pos &&
-                            (window <= 0 || base >= max_pos + 1 - window) && wr1 - wr0 == 15;
+                            base >= first_key(max_pos, window) && wr1 - wr0 == 15;
       float tmax[2] = {-INFINITY, -INFINITY};
       if (interior) {
 #pragma unroll
@@ -318,7 +318,7 @@ LLM_EXPORT int llm_attention_flash(const void* q, void* out, float* part_o, floa
                                    int page_size, float scale, int window, int splits,
                                    cudaStream_t stream) {
   if (n_items <= 0) return 0;
-  if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || splits < 1 || splits > 65535 || page_size <= 0 || window < 0)
+  if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || splits < 1 || splits > 65535 || page_size <= 0)
     return LLM_ERR_ARGUMENT;
   if (splits > 1 && (!part_o || !part_ml)) return LLM_ERR_ARGUMENT;
   // a CTA holds rows_per_cta (token, head) pairs and every head of a group belongs to one CTA:

@@ -1,6 +1,6 @@
 // Paged causal attention over the cache for any mix of rows: one warp per (row, query head).
 //   s_p = dot(q, K[p]) * scale for the keys p of the row's own request with lo <= p <= pos,
-//   lo = max(0, pos + 1 - window) when a window is set; softmax and the weighted sum of V in
+//   lo = first_key(pos, window) (a sliding window, or the query's own chunk); softmax and the weighted sum of V in
 //   32-bit with a running maximum.
 // Keys are visited in tiles of 32 aligned to absolute positions, each lane scoring one key, so
 // the order of every sum depends only on positions: the result for a row is the same however the
@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
   const int kvh = h / (Hq / Hkv);
   const int pos = row_pos[t];
   const int* table = block_table + (size_t)row_slot[t] * table_stride;
-  const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  const int lo = first_key(pos, window);
 
   float* qs = q_s[warp_in_block];
   const T* qrow = q + ((size_t)t * Hq + h) * hd;

@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
   const int kvh = blockIdx.y;
   const int G = Hq / Hkv;
   const int hi = it.pos_start + it.tokens - 1;
-  const int lo = (window > 0 && it.pos_start + 1 > window) ? it.pos_start + 1 - window : 0;
+  const int lo = first_key(it.pos_start, window);
   const int tile_first = lo / KT;
   const int ntiles = hi / KT - tile_first + 1;
 
@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
     const int tok = row / G, head = kvh * G + row % G;
     const bool rvalid = tok < it.tokens;
     const int rpos = it.pos_start + tok;
-    const int rlo = (window > 0 && rpos + 1 > window) ? rpos + 1 - window : 0;
+    const int rlo = first_key(rpos, window);
     const uint32_t pair_bar = 2 + q4;                    // named barrier of the two warps of a quarter
     const uint32_t x_addr = tmem + lane_base + O_COL + HD;   // spare columns: the sums of the two halves of a row meet here
     float m_used = -INFINITY, l = 0.f;
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
       const int c_lo = max(0, rlo - base);
       // a tile that every row of the CTA sees completely needs no per-key tests
       const bool interior = it.tokens * G >= ROWS && base + KT - 1 <= it.pos_start &&
-                            (window <= 0 || base >= hi + 1 - window);
+                            base >= first_key(hi, window);
       // ---- this thread's scores into registers (one round trip to tensor memory)
       uint32_t v[COLS];
 #pragma unroll
@@ -462,7 +462,7 @@ __device__ __forceinline__ bool work_at(int round, const int* __restrict__ items
   w.it = reinterpret_cast<const Item*>(items)[n_items - 1 - idx / Hkv];
   w.kvh = idx % Hkv;
   w.hi = w.it.pos_start + w.it.tokens - 1;
-  w.lo = (window > 0 && w.it.pos_start + 1 > window) ? w.it.pos_start + 1 - window : 0;
+  w.lo = first_key(w.it.pos_start, window);
   w.tile_first = w.lo / KT;
   w.ntiles = w.hi / KT - w.tile_first + 1;
   return true;
@@ -652,7 +652,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
       const int tok = row / G, head = w.kvh * G + row % G;
       const bool rvalid = tok < w.it.tokens;
       const int rpos = w.it.pos_start + tok;
-      const int rlo = (window > 0 && rpos + 1 > window) ? rpos + 1 - window : 0;
+      const int rlo = first_key(rpos, window);
       float m_used = -INFINITY, l = 0.f;
       for (int j = 0; j < w.ntiles; ++j, ++T) {
         const int b = (int)(T & 1);
@@ -668,7 +668,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
         const int c_hi = rvalid ? min(KT - 1, rpos - base) : -1;
         const int c_lo = max(0, rlo - base);
         const bool interior = w.it.tokens * G >= ROWS && base + KT - 1 <= w.it.pos_start &&
-                              (window <= 0 || base >= w.hi + 1 - window);
+                              base >= first_key(w.hi, window);
         uint32_t v[COLS];
 #pragma unroll
         for (int c = 0; c < COLS; c += 32) tmem_ld32(s_addr + c0 + c, v + c);

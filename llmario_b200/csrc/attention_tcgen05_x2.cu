@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_x2_kernel(
   const int tok_a = it.tokens < cap ? it.tokens : cap;       // tokens of tile A
   const int tok_b = it.tokens - tok_a;                       // tokens of tile B (0: there is none)
   const int hi_a = it.pos_start + tok_a - 1, hi_b = it.pos_start + it.tokens - 1;
-  const int lo = (window > 0 && it.pos_start + 1 > window) ? it.pos_start + 1 - window : 0;
+  const int lo = first_key(it.pos_start, window);
   const int tile_first = lo / KT;
   const int nt_a = hi_a / KT - tile_first + 1;               // key tiles of A
   const int nt_b = tok_b > 0 ? hi_b / KT - tile_first + 1 : 0;
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_x2_kernel(
     const int nt_x = x ? nt_b : nt_a;
     const bool rvalid = tok < tokens_x;
     const int rpos = it.pos_start + first_tok + tok;
-    const int rlo = (window > 0 && rpos + 1 > window) ? rpos + 1 - window : 0;
+    const int rlo = first_key(rpos, window);
     const int pos0 = it.pos_start + first_tok;        // first position of the tile
     const uint32_t s_addr = tmem + lane_base + (uint32_t)x * S_COLS;
     const uint32_t o_addr = tmem + lane_base + O_COL + (uint32_t)x * O_COLS;
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_x2_kernel(
       const int c_lo = max(0, rlo - base);
       // a tile that every row of the query tile sees completely needs no per-key tests
       const bool interior = tokens_x * G >= ROWS && base + KT - 1 <= pos0 &&
-                            (window <= 0 || base >= pos0 + tokens_x - window);
+                            base >= first_key(pos0 + tokens_x - 1, window);
       uint32_t v[KT];
 #pragma unroll
       for (int c = 0; c < KT; c += 32) tmem_ld32(s_addr + c, v + c);

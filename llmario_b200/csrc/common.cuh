@@ -50,6 +50,16 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// The lowest key position that a query at position p sees, for the one integer by which every
+// attention kernel is told its mask.  window > 0: the last `window` keys (sliding window).
+// window < 0: the keys of the query's own chunk of -window positions, chunks counted from
+// position 0 of the sequence.  window == 0: every earlier key.  Non-decreasing in p.
+__host__ __device__ __forceinline__ int first_key(int p, int window) {
+  if (window > 0) return p + 1 > window ? p + 1 - window : 0;
+  if (window < 0) return p - p % (-window);
+  return 0;
+}
+
 // ---- mbarriers (shared by the kernels that move data with the TMA unit)
 constexpr long long WAIT_CYCLES = 4000000000LL;   // bound of every wait: about two seconds
 

@@ -353,3 +353,93 @@ LLM_EXPORT int llm_selftest_wait_gives_up(int* status, long long limit_cycles, c
   selftest_wait_kernel<<<1, 32, 0, stream>>>(status, limit_cycles);
   return launch_status();
 }
+
+// out[r][c] = x[r][c] rounded to the output type, for a [rows][cols] window of two matrices with
+// their own row strides (the 32-bit residual stream as a sublayer's input; a slice of a
+// projection's 32-bit output as the next product's operand).
+template <typename TOut>
+__global__ void cast_rows_kernel(const float* __restrict__ x, long long x_stride, TOut* __restrict__ out,
+                                 long long out_stride, int rows, int cols) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = (long long)rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols, c = i - r * cols;
+    out[r * out_stride + c] = from_f32<TOut>(x[r * x_stride + c]);
+  }
+}
+
+LLM_EXPORT int llm_cast_rows(const float* x, long long x_stride, void* out, int out_dtype,
+                             long long out_stride, int rows, int cols, cudaStream_t stream) {
+  const long long total = (long long)rows * cols;
+  if (total <= 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
+  if (out_dtype == LLM_F32)
+    return launch_pdl(cast_rows_kernel<float>, blocks, 256, 0, stream, x, x_stride, (float*)out, out_stride, rows, cols);
+  if (out_dtype == LLM_BF16)
+    return launch_pdl(cast_rows_kernel<bf16>, blocks, 256, 0, stream, x, x_stride, (bf16*)out, out_stride, rows, cols);
+  return LLM_ERR_UNSUPPORTED;
+}
+
+// x[r][:] += y[r][:] * rsqrt(mean(y[r]^2) + eps) * w[:] * s[:]: the norm of a sublayer's output,
+// a scale per channel (s may be null), and the residual sum, all in 32-bit.
+__global__ void norm_scale_add_kernel(const float* __restrict__ y, const float* __restrict__ w,
+                                      const float* __restrict__ s, float* __restrict__ x, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const size_t r = blockIdx.x;
+  const float* yr = y + r * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = yr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = yr[i] * scale * w[i];
+    if (s) v *= s[i];
+    x[r * width + i] += v;
+  }
+}
+
+LLM_EXPORT int llm_norm_scale_add(const float* y, const float* w, const float* s, float* x, int rows,
+                                  int width, float eps, cudaStream_t stream) {
+  if (rows <= 0 || width <= 0) return 0;
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  return launch_pdl(norm_scale_add_kernel, rows, threads, 0, stream, y, w, s, x, width, eps);
+}
+
+// out[r][h][:] *= sigmoid(gate[r * gate_stride + h]): one gate per (row, head) on the output of
+// attention, in 32-bit, rounded once.  With `clear` the gates that were read are zeroed (they
+// lie in a buffer that a split-K product adds into).
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ out, float* __restrict__ gate, int gate_stride, int rows,
+                                 int H, int hd, int clear) {
+  pdl_trigger();
+  pdl_wait();
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)rows * H) return;
+  const int r = (int)(item / H), h = (int)(item % H), lane = threadIdx.x & 31;
+  float* gp = gate + (size_t)r * gate_stride + h;
+  const float z = *gp;
+  __syncwarp();
+  if (clear && lane == 0) *gp = 0.f;
+  const float sg = 1.f / (1.f + expf(-z));
+  T* o = out + ((size_t)r * H + h) * hd;
+  for (int i = lane; i < hd; i += 32) o[i] = from_f32<T>(to_f32(o[i]) * sg);
+}
+
+LLM_EXPORT int llm_head_gate(void* out, int dtype, float* gate, int gate_stride, int rows, int H, int hd,
+                             int clear, cudaStream_t stream) {
+  const long long items = (long long)rows * H;
+  if (items <= 0) return 0;
+  const int blocks = (int)((items + 3) / 4);
+  if (dtype == LLM_F32)
+    return launch_pdl(head_gate_kernel<float>, blocks, 128, 0, stream, (float*)out, gate, gate_stride, rows, H, hd, clear);
+  if (dtype == LLM_BF16)
+    return launch_pdl(head_gate_kernel<bf16>, blocks, 128, 0, stream, (bf16*)out, gate, gate_stride, rows, H, hd, clear);
+  return LLM_ERR_UNSUPPORTED;
+}

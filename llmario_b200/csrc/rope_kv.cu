@@ -9,7 +9,8 @@
 
 namespace {
 // One warp per (row, head).  Heads 0..Hq-1 are queries, Hq..Hq+Hkv-1 keys, then Hkv values.
-// proj row layout: [Hq*hd | Hkv*hd | Hkv*hd] (keys and values absent when !has_kv).
+// proj row layout: [Hq*hd | Hkv*hd | Hkv*hd] (keys and values absent when !has_kv; has_kv == 2:
+// no value heads are projected, every key head is also stored, as projected, as its value head).
 template <typename TQ, typename TC>
 __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ proj, int proj_stride, TQ* __restrict__ q_out,
@@ -25,7 +26,7 @@ __global__ void qk_norm_rope_store_kernel(
   const int t = blockIdx.x;
   const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  const int heads = Hq + (has_kv ? 2 * Hkv : 0);
+  const int heads = Hq + (has_kv == 1 ? 2 * Hkv : has_kv == 2 ? Hkv : 0);
   if (h >= heads) return;
   float* src = const_cast<float*>(proj) + (size_t)t * proj_stride + h * hd;
   const int pos = row_pos[t];
@@ -42,6 +43,10 @@ __global__ void qk_norm_rope_store_kernel(
     const int kvh = is_k ? h - Hq : h - Hq - Hkv;
     TC* base = is_k ? k_cache : v_cache;
     cache_dst = base + (size_t)page * page_stride + (size_t)(kvh * page_size + in_page) * hd;
+    if (has_kv == 2) {   // the values are the keys as projected: stored before norm and rotation
+      TC* v_dst = v_cache + (size_t)page * page_stride + (size_t)(kvh * page_size + in_page) * hd;
+      for (int i = lane; i < hd; i += 32) v_dst[i] = from_f32<TC>(src[i]);
+    }
   }
   if (h >= Hq + Hkv) {  // value: copy
     if (hd == 128 && sizeof(TC) == 2 && !(proj_stride & 3)) {      // four elements per lane
@@ -214,9 +219,9 @@ LLM_EXPORT int llm_qk_norm_rope_store(
     int page_size, float eps, int has_kv, int use_norm, int clear_proj, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (rot_dim > hd || (rot_dim & 1)) return LLM_ERR_ARGUMENT;
-  const int heads = Hq + (has_kv ? 2 * Hkv : 0);
+  const int heads = Hq + (has_kv == 1 ? 2 * Hkv : has_kv == 2 ? Hkv : 0);
   const int threads = 128;
-  if (rows >= 256 && dtype == LLM_BF16 && hd == 128 && rot_dim == 128 && cos_sin && !clear_proj &&
+  if (rows >= 256 && has_kv != 2 && dtype == LLM_BF16 && hd == 128 && rot_dim == 128 && cos_sin && !clear_proj &&
       !(proj_stride & 1) && !(((uintptr_t)proj | (uintptr_t)cos_sin) & 15)) {
     const int rc = launch_pdl(qk_norm_rope_store_rows_kernel, dim3(rows, (heads + 15) / 16), threads, 0, stream,
                               proj, proj_stride, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, page_stride,

@@ -96,6 +96,12 @@ int llm_attention_tcgen05_x2(const void* q, void* out, int rows, const void* k_c
 }
 
 namespace {
+// How many keys a query of the step sees at most under the mask that `window` encodes (see
+// first_key): the window's or the chunk's size, or every position up to the largest one.
+inline int reach_of(int window, int max_pos) {
+  const int w = window < 0 ? -window : window;
+  return w && w < max_pos + 1 ? w : max_pos + 1;
+}
 
 // ------------------------------------------------------------------------------------------------
 // policies (the same numbers as llmario_b200/kernels.py)
@@ -424,7 +430,7 @@ struct Run {
         else direct.insert(direct.end(), {it[0], it[1], it[2], it[3]});
       }
       if (!take) continue;
-      const int lo = window > 0 && r.pos0 + 1 > window ? r.pos0 + 1 - window : 0;
+      const int lo = first_key(r.pos0, window);
       const int first_page = lo / D;                        // scratch page of the lowest key read
       const int first_pos = first_page * D;
       const int n_pages = (r.pos1 - 1) / D - first_page + 1;
@@ -470,7 +476,7 @@ struct Run {
     const bool ok = st.dtype == LLM_BF16 && cos_sin != nullptr && L.rot_dim == L.head_dim &&
                     L.num_heads / L.num_kv_heads <= 8 && decode_tma_ok(c, L.head_dim) && st.all_single;
     if (!ok || g_fuse_mode == 1) return ok;
-    const int reach = L.window ? (st.max_pos + 1 < L.window ? st.max_pos + 1 : L.window) : st.max_pos + 1;
+    const int reach = reach_of(L.window, st.max_pos);
     const int resident = DECODE_TMA_CTAS_PER_SM * sm_count();
     return (long long)st.rows * L.num_kv_heads *
                llm_decode_splits(st.rows, L.num_kv_heads, reach, resident, DECODE_TMA_TILE) <=
@@ -505,7 +511,7 @@ struct Run {
     const Plan* plan = nullptr;
     int rc = plan_for(group, (x2 ? 256 : tc ? 128 : 64) / group, &plan);
     if (rc) return rc;
-    const int reach = window ? (st.max_pos + 1 < window ? st.max_pos + 1 : window) : st.max_pos + 1;
+    const int reach = reach_of(window, st.max_pos);
     if (plan->n_small) {
       const bool tma = group <= 8 && decode_tma_ok(c, hd);
       const int splits = plan->small_single
@@ -621,7 +627,7 @@ struct Run {
     if (rc) return rc;
     const bool use_norm = L.q_norm_w != nullptr;
     if (fusion_ok(L, c, cos_sin)) {
-      const int reach = L.window ? (st.max_pos + 1 < L.window ? st.max_pos + 1 : L.window) : st.max_pos + 1;
+      const int reach = reach_of(L.window, st.max_pos);
       const int splits = llm_decode_splits(rows, Hkv, reach, DECODE_TMA_CTAS_PER_SM * sm_count(), DECODE_TMA_TILE);
       float *part_o, *part_ml;
       rc = parts(splits, L, &part_o, &part_ml);

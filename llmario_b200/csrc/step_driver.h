@@ -11,7 +11,7 @@ extern "C" {
 struct LlmLayerDesc {
   int hidden;
   int num_heads, num_kv_heads, head_dim;
-  int window;              // 0: every earlier key
+  int window;              // 0: every earlier key; > 0: the last `window` keys; < 0: the query's own chunk of -window
   int rot_dim;             // 0: no rotation
   int intermediate;
   int interleaved;         // gate and up rows stored as alternating blocks of 16

@@ -31,7 +31,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                     help="most tokens that live requests hold at any time (each request's "
                          "count rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=64, help="tokens in a cache page")
-    ap.add_argument("--max-requests", type=int, default=8, help="request slots")
+    ap.add_argument("--max-requests", type=int, default=4,
+                    help="request slots (live requests at any time)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     if args.page_size <= 0 or 64 % args.page_size != 0 and args.page_size % 64 != 0:

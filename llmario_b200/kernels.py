@@ -70,6 +70,14 @@ def _signatures():
         "llm_apply_penalties": [P, L, I, P, I, P, P, P, P, P, I, P],
         "llm_random_normal": [P, I, L, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, L,
                               P],
+        "llm_cast_rows": [P, L, P, I, L, I, I, P],
+        "llm_norm_scale_add": [P, P, P, P, I, I, F, P],
+        "llm_head_gate": [P, I, P, I, I, I, I, I, P],
+        "llm_segment_table": [P, I, P, I, P],
+        "llm_linear_recurrence": [P, I, P, I, P, I, P, I, P, P, F, F, P, L, P, I, P, P, I, I, I, I,
+                                  I, I, I, I, P],
+        "llm_causal_conv_silu": [P, I, P, P, P, L, P, P, I, I, I, P, I, I, I, P],
+        "llm_gated_group_norm": [P, I, P, I, P, I, P, I, P, I, P, I, I, I, I, I, F, I, P],
     }
 
 
@@ -246,14 +254,17 @@ def qk_norm_rope_store(proj: torch.Tensor, q_out: torch.Tensor,
                        k_norm_w: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
                        attn_factor: float, num_heads: int, num_kv_heads: int, head_dim: int,
                        rot_dim: int, page_size: int, eps: float,
-                       cos_sin: Optional[torch.Tensor] = None, clear_proj: bool = False) -> None:
+                       cos_sin: Optional[torch.Tensor] = None, clear_proj: bool = False,
+                       values_are_keys: bool = False) -> None:
     """Per-head norm, rotation and stores for the rows of ``proj`` (float32,
-    [rows, (Hq + 2 Hkv) * hd], or [rows, Hq * hd] when no cache is given)."""
+    [rows, (Hq + 2 Hkv) * hd], or [rows, Hq * hd] when no cache is given).  With
+    ``values_are_keys`` the rows hold no values ([rows, (Hq + Hkv) * hd]): every key head is
+    stored twice, normed and rotated as the key and as projected as the value."""
     _cuda(proj, q_out, k_cache, v_cache, block_table, row_slot, row_pos, q_norm_w, k_norm_w,
           inv_freq)
     assert proj.dtype == torch.float32 and proj.stride(1) == 1
     rows = proj.shape[0]
-    has_kv = k_cache is not None
+    has_kv = 0 if k_cache is None else (2 if values_are_keys else 1)
     use_norm = q_norm_w is not None
     if rot_dim > 0:
         assert inv_freq is not None and inv_freq.dtype == torch.float32
@@ -322,6 +333,135 @@ def apply_penalties(logits: torch.Tensor, triples: torch.Tensor, n: int, repeat:
                                      n, _ptr(repeat), _ptr(freq), _ptr(presence),
                                      _ptr(inflight_src), _ptr(drawn), logits.shape[0], _stream()),
            "apply_penalties")
+
+
+def mask_code(window: Optional[int] = None, chunk: Optional[int] = None) -> int:
+    """The one integer by which the attention kernels are told which earlier keys a query sees:
+    0 all of them, ``window`` > 0 the last ``window``, ``-chunk`` the keys of the query's own
+    chunk of ``chunk`` positions (chunks counted from position 0 of the sequence)."""
+    if window and chunk:
+        raise KernelError("a sliding window and a chunked mask exclude each other")
+    if (window or 0) < 0 or (chunk or 0) < 0:
+        raise KernelError("window and chunk sizes are positive")
+    return int(window) if window else (-int(chunk) if chunk else 0)
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x rounded to out's type; both [rows, cols] with unit stride along a row (either
+    may be a column slice of a wider matrix); x float32."""
+    _cuda(x, out)
+    assert x.dtype == torch.float32 and x.shape == out.shape and x.dim() == 2
+    assert x.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().llm_cast_rows(_ptr(x), x.stride(0), _ptr(out), _dt(out), out.stride(0),
+                               x.shape[0], x.shape[1], _stream()), "cast_rows")
+
+
+def norm_scale_add(y: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor],
+                   x: torch.Tensor, eps: float) -> None:
+    """x += y * rsqrt(mean(y^2) + eps) * weight (* scale): all float32, row by row."""
+    _cuda(y, weight, scale, x)
+    assert y.dtype == x.dtype == weight.dtype == torch.float32 and y.shape == x.shape
+    assert y.is_contiguous() and x.is_contiguous() and weight.numel() == x.shape[1]
+    assert scale is None or (scale.dtype == torch.float32 and scale.numel() == x.shape[1])
+    _check(lib().llm_norm_scale_add(_ptr(y), _ptr(weight), _ptr(scale), _ptr(x), x.shape[0],
+                                    x.shape[1], float(eps), _stream()), "norm_scale_add")
+
+
+def head_gate(out: torch.Tensor, gate: torch.Tensor, num_heads: int, head_dim: int,
+              clear: bool = False) -> None:
+    """out[r, h, :] *= sigmoid(gate[r, h]); ``gate`` float32 [rows, heads] (a column slice of a
+    wider matrix is fine), zeroed after use with ``clear``."""
+    _cuda(out, gate)
+    assert gate.dtype == torch.float32 and gate.stride(1) == 1 and out.is_contiguous()
+    rows = out.shape[0]
+    assert gate.shape == (rows, num_heads) and out.shape[1] == num_heads * head_dim
+    _check(lib().llm_head_gate(_ptr(out), _dt(out), _ptr(gate), gate.stride(0), rows, num_heads,
+                               head_dim, int(clear), _stream()), "head_gate")
+
+
+def segment_table(row_slot: torch.Tensor, seg: torch.Tensor) -> None:
+    """seg[s] = (first row, row after the last) of the step's rows whose request slot is s,
+    (0, 0) for a slot without rows; int32 [slots, 2], made on the device from ``row_slot``."""
+    _cuda(row_slot, seg)
+    assert row_slot.dtype == torch.int32 and seg.dtype == torch.int32 and seg.is_contiguous()
+    _check(lib().llm_segment_table(_ptr(row_slot), row_slot.numel(), _ptr(seg), seg.shape[0],
+                                   _stream()), "segment_table")
+
+
+DECAY_VECTOR, DECAY_SIGMOID_POW, DECAY_RATE_STEP = 0, 1, 2
+
+
+def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch.Tensor,
+                      state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor,
+                      seg: Optional[torch.Tensor], heads: int, groups: int, key_dim: int,
+                      value_dim: int, kind: int, q_scale: float = 1.0, exponent: float = 1.0,
+                      rate_log: Optional[torch.Tensor] = None,
+                      step_bias: Optional[torch.Tensor] = None) -> None:
+    """Per request and head ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_scale q_t)`` over
+    the rows of the step in order.  q, k float32 [rows, groups * key_dim], v and out float32
+    [rows, heads * value_dim] (column slices of wider matrices are fine); head h uses group
+    ``h // (heads // groups)``.  ``state``: float32 [slots, >= heads * value_dim * key_dim], each
+    head's [value_dim, key_dim] block, carried from step to step.  ``kind`` says how the decay
+    comes from ``d``: DECAY_VECTOR ``a = d`` and DECAY_SIGMOID_POW ``a = sigmoid(d)^exponent``
+    with d [rows, heads * key_dim]; DECAY_RATE_STEP with d [rows, heads]:
+    ``step = softplus(d + step_bias[h])``, ``a = exp(-exp(rate_log[h]) step)`` and v is
+    multiplied by step.  ``seg``: the table of :func:`segment_table`, or None when every row
+    is a request of its own."""
+    _cuda(q, k, v, d, state, out, row_slot, seg, rate_log, step_bias)
+    for t in (q, k, v, d, state, out):
+        assert t.dtype == torch.float32 and t.stride(-1) == 1
+    rows = out.shape[0]
+    assert state.dim() == 2 and state.shape[1] >= heads * value_dim * key_dim
+    _check(lib().llm_linear_recurrence(
+        _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(d), d.stride(0),
+        _ptr(rate_log), _ptr(step_bias), float(exponent), float(q_scale), _ptr(state),
+        state.stride(0), _ptr(out), out.stride(0), _ptr(seg), _ptr(row_slot), rows,
+        state.shape[0], int(seg is None), heads, groups, key_dim, value_dim, kind, _stream()),
+        f"linear_recurrence (key_dim {key_dim})")
+
+
+def causal_conv_silu(src: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                     history: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor,
+                     seg: Optional[torch.Tensor]) -> None:
+    """out[r, c] = silu(bias[c] + sum_j weight[c, taps-1-j] * input(r - j, c)) over each
+    request's own tokens; inputs before the step come from ``history`` (float32
+    [slots, >= channels * (taps - 1)], each channel's last taps - 1 inputs, oldest first), which
+    is brought up to date afterwards.  src, out float32 [rows, channels] (column slices are
+    fine); weight float32 [channels, taps]."""
+    _cuda(src, weight, bias, history, out, row_slot, seg)
+    for t in (src, weight, history, out):
+        assert t.dtype == torch.float32 and t.stride(-1) == 1
+    rows, channels = out.shape
+    taps = weight.shape[1]
+    assert weight.is_contiguous() and weight.shape[0] == channels and src.shape == out.shape
+    assert history.shape[1] >= channels * (taps - 1)
+    _check(lib().llm_causal_conv_silu(
+        _ptr(src), src.stride(0), _ptr(weight), _ptr(bias), _ptr(history), history.stride(0),
+        _ptr(row_slot), _ptr(seg), rows, history.shape[0], int(seg is None), _ptr(out),
+        out.stride(0), channels, taps, _stream()), "causal_conv_silu")
+    global launches
+    launches += int(taps > 1)      # the history is brought up to date by a launch of its own
+
+
+def gated_group_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor,
+                     out: torch.Tensor, group: int, eps: float, gate_first: bool,
+                     skip: Optional[torch.Tensor] = None, skip_input: Optional[torch.Tensor] = None,
+                     head: int = 0) -> None:
+    """The recurrence's output through its gate and a norm over groups of ``group`` channels:
+    ``y = o (+ skip[ch // head] * skip_input)``; with ``gate_first``
+    ``out = unit(y * silu(gate)) * weight`` else ``out = unit(y) * weight * silu(gate)``, where
+    unit divides each group by its root mean square.  ``weight`` is indexed by the channel
+    modulo its length.  o, gate, skip_input float32 [rows, channels] (column slices are fine)."""
+    _cuda(o, gate, weight, out, skip, skip_input)
+    rows, channels = out.shape
+    assert o.dtype == gate.dtype == weight.dtype == torch.float32 and channels % group == 0
+    assert o.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1
+    assert (skip is None) == (skip_input is None)
+    _check(lib().llm_gated_group_norm(
+        _ptr(o), o.stride(0), _ptr(skip_input), skip_input.stride(0) if skip is not None else 0,
+        _ptr(skip), head, _ptr(gate), gate.stride(0), _ptr(weight), weight.numel(), _ptr(out),
+        _dt(out), out.stride(0), rows, channels // group, group, float(eps), int(gate_first),
+        _stream()), "gated_group_norm")
 
 
 def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0) -> None:

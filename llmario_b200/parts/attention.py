@@ -5,6 +5,15 @@ Order of operations as in crates/engine/model/src/forward.rs:399-485: project q,
 head of q and k; rotate q and k by position; store k and v in the cache; attend from the cache
 (causal, optionally only the last ``window`` keys); project the result and add it to the
 residual stream.  A call that reads another call's cache projects only q.
+
+Options that are data of the part's spec (each absent by default):
+
+* ``chunk``: a query sees only the earlier keys of its own chunk of ``chunk`` positions, chunks
+  counted from position 0 of the sequence (excludes ``window``);
+* ``values: "keys"``: there is no value projection; a key head's value is the key as projected
+  (with its bias), before the per-head norm and the rotation;
+* tensor role ``gate`` ([heads, hidden]): head h's output is multiplied by the sigmoid of the
+  h-th gate, a projection of the mixer's own input, before the output projection.
 """
 from __future__ import annotations
 
@@ -30,6 +39,11 @@ class Attention:
         self.head_dim = int(spec["head_dim"])
         self.scale = float(spec["scale"])
         self.window = spec.get("window")
+        self.chunk = spec.get("chunk")
+        self.mask = kernels.mask_code(self.window, self.chunk)   # what the kernels are told
+        if spec.get("values", "projected") not in ("projected", "keys"):
+            raise ConfigError(f"attention: values '{spec.get('values')}' (projected or keys)")
+        self.values_are_keys = spec.get("values") == "keys"
         refusal = kernels.attention_refusal(self.num_heads, self.num_kv_heads, self.head_dim)
         if refusal is not None:      # now, when the model is built, not at its first step
             raise ConfigError(f"attention: {refusal}")
@@ -44,7 +58,13 @@ class Attention:
             raise ValueError("q_norm and k_norm come together")
         if self.q_norm is not None and self.q_norm.eps != self.k_norm.eps:
             raise ValueError("q_norm and k_norm must share eps")
-        w = {r: tensor_of(spec, r, weights) for r in ("q", "k", "v")}
+        w = {r: tensor_of(spec, r, weights) for r in ("q", "k")}
+        if not self.values_are_keys:
+            w["v"] = tensor_of(spec, "v", weights)
+        gate = optional_tensor_of(spec, "gate", weights)
+        if gate is not None and tuple(gate.shape) != (self.num_heads, self.hidden):
+            raise ConfigError(f"attention: a gate of {list(gate.shape)} for {self.num_heads} "
+                              f"heads of a width of {self.hidden}")
         # biases exist for the families that store them (forward.rs:399-425); tensor roles
         # "q_bias", "k_bias", "v_bias", "o_bias", each optional
         b = {r: optional_tensor_of(spec, r + "_bias", weights) for r in ("q", "k", "v", "o")}
@@ -63,19 +83,38 @@ class Attention:
             for norm in (self.q_norm, self.k_norm):
                 if norm is not None:
                     norm.weight = norm.weight[perm].contiguous()
-        self.qkv_proj = Linear.stacked([w["q"], w["k"], w["v"]], [b["q"], b["k"], b["v"]])
+        # one product for everything that reads the mixer's input: q, k, v (unless the values
+        # are the keys), the gates; its rows padded to a multiple of 16 so that the 32-bit
+        # output keeps rows of whole 16-byte units
+        mats = [w["q"], w["k"]] + ([] if self.values_are_keys else [w["v"]])
+        biases = [b["q"], b["k"]] + ([] if self.values_are_keys else [b["v"]])
+        self.kv_cols = self.kv_width * (1 if self.values_are_keys else 2)
+        self.gate_col = None
+        if gate is not None:
+            self.gate_col = self.q_width + self.kv_cols
+            mats.append(gate)
+            biases.append(None)
+        n_rows = sum(m.shape[0] for m in mats)
+        if n_rows % 16:
+            mats.append(torch.zeros(16 - n_rows % 16, self.hidden, dtype=mats[0].dtype,
+                                    device=mats[0].device))
+            biases.append(None)
+        self.qkv_proj = Linear.stacked(mats, biases)
         self.q_proj = Linear(self.qkv_proj.weight[:self.q_width],      # the first rows, no copy
                              None if self.qkv_proj.bias is None else self.qkv_proj.bias[:self.q_width])
         self.o_proj = Linear(tensor_of(spec, "o", weights), b["o"])
 
     def cache_need(self):
-        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+        # (no query ever looks back further than a chunk is long: pages behind that go back)
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window or self.chunk)
 
     def streamed_weights(self):
         """The matrices a step reads once: q, k, v (stacked) and the output projection."""
         return [self.qkv_proj.weight, self.o_proj.weight]
 
-    def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor) -> None:
+    def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        """Adds the result into ``x``; with ``accumulate=False`` ``x`` (float32) receives it."""
         rows = ctx.rows
         view = ctx.cache.view(call.cache_entry)
         if view is None:
@@ -83,11 +122,14 @@ class Attention:
         # With few rows the product is cut along K and its partial sums are added into the
         # buffer.  That buffer is created as zeros and the kernel that consumes it clears what it
         # read, which saves a clearing pass per layer.
-        width = self.q_width + (2 * self.kv_width if call.writes_cache else 0)
+        whole = call.writes_cache or self.gate_col is not None
+        width = self.qkv_proj.out_features if whole else self.q_width
         kept_zero = rows <= kernels.SPLIT_K_MAX_ROWS
         proj = ctx.buffer("attn.proj.%s%d" % ("z" if kept_zero else "", width), (rows, width),
                           torch.float32, zero=kept_zero)
-        (self.qkv_proj if call.writes_cache else self.q_proj)(h, proj, out_is_zero=kept_zero)
+        (self.qkv_proj if whole else self.q_proj)(h, proj, out_is_zero=kept_zero)
+        if whole and not call.writes_cache and kept_zero:
+            proj[:, self.q_width:self.q_width + self.kv_cols].zero_()    # keys nobody consumes
         tables = self.position.rotary_tables() if self.position is not None else None
         if self.position is not None and tables is None:
             raise NotImplementedError("a position encoding that is not a rotation needs its own "
@@ -97,8 +139,9 @@ class Attention:
             else None
         out = ctx.buffer("attn.out", (rows, self.q_width))
         q = ctx.buffer("attn.q", (rows, self.q_width))
-        if kernels.decode_fusion_ok(ctx, view, self.num_heads, self.num_kv_heads, self.head_dim,
-                                    rot_dim, angles, self.window):
+        plain = not self.values_are_keys and self.gate_col is None and self.chunk is None
+        if plain and kernels.decode_fusion_ok(ctx, view, self.num_heads, self.num_kv_heads,
+                                              self.head_dim, rot_dim, angles, self.window):
             # a step of single new tokens: norm, rotation, cache write and attention in one kernel
             kernels.attention_decode_fused(
                 ctx, proj, out, view, call.writes_cache,
@@ -106,7 +149,7 @@ class Attention:
                 self.k_norm.weight if self.k_norm is not None else None, angles,
                 self.q_norm.eps if self.q_norm is not None else 0.0, kept_zero, self.num_heads,
                 self.num_kv_heads, self.head_dim, self.scale, self.window)
-            self.o_proj(out, x, accumulate=True)
+            self.o_proj(out, x, accumulate=accumulate)
             return
         kernels.qk_norm_rope_store(
             proj, q, view.k if call.writes_cache else None,
@@ -116,10 +159,13 @@ class Attention:
             self.k_norm.weight if self.k_norm is not None else None,
             inv_freq, attn_factor, self.num_heads, self.num_kv_heads, self.head_dim, rot_dim,
             view.page_size, self.q_norm.eps if self.q_norm is not None else 0.0, angles,
-            clear_proj=kept_zero)
+            clear_proj=kept_zero, values_are_keys=self.values_are_keys)
         driver.attention(ctx, q, out, view, self.num_heads, self.num_kv_heads, self.head_dim,
-                         self.scale, self.window)
-        self.o_proj(out, x, accumulate=True)
+                         self.scale, self.mask)
+        if self.gate_col is not None:
+            kernels.head_gate(out, proj[:, self.gate_col:self.gate_col + self.num_heads],
+                              self.num_heads, self.head_dim, clear=kept_zero)
+        self.o_proj(out, x, accumulate=accumulate)
 
 
 register_part("mixer", "attention", Attention, replace=True)

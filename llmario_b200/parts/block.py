@@ -1,15 +1,17 @@
 """Pre-norm residual arrangement: ``x += mixer(norm(x)); x += feed_forward(norm(x))``
-(crates/engine/model/src/forward.rs:356-362).  The residual stream ``x`` is 32-bit in every
-mode; the parts add into it."""
+(crates/engine/model/src/forward.rs:356-362), and the arrangement with the norm on the
+sublayer's output.  The residual stream ``x`` is 32-bit in every mode; the parts add into it."""
 from __future__ import annotations
 
 from typing import Dict
 
 import torch
 
-from ..config.spec import LayerSpec, PartSpec
-from .base import (BoundCall, StepContext, build_part, graph_safe, register_part,
-                   streamed_weights_of)
+from .. import kernels
+from ..config.spec import ConfigError, LayerSpec, PartSpec
+from .base import (BoundCall, StepContext, build_part, graph_safe, optional_tensor_of,
+                   register_part, streamed_weights_of)
+from .norm import RmsNorm
 
 
 class PreNormResidualBlock:
@@ -43,4 +45,62 @@ class PreNormResidualBlock:
         self.feed_forward.forward(ctx, h, x)
 
 
+class OutputNormResidualBlock:
+    """Norm on the sublayer's output only, with a scale per channel:
+    ``x += s1 * norm1(mixer(x)); x += s2 * norm2(feed_forward(x))``.  The sublayers read the
+    residual stream itself (rounded to the activation type); norm, scale and sum are 32-bit and
+    one kernel.  A layer whose feed-forward is of kind ``none`` has only the first sublayer; the
+    scales (tensor roles ``mixer_scale`` / ``feed_forward_scale``) are optional."""
+
+    def __init__(self, spec: PartSpec, layer: LayerSpec, weights: Dict[str, torch.Tensor],
+                 dtype, device):
+        def scale(role):
+            t = optional_tensor_of(spec, role, weights) if spec.get("tensors") else None
+            return None if t is None else t.to(device=device, dtype=torch.float32).contiguous()
+
+        self.mixer_norm = build_part("norm", spec["mixer_norm"], weights, dtype, device)
+        self.mixer_scale = scale("mixer_scale")
+        self.mixer = build_part("mixer", layer.mixer, weights, dtype, device)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, dtype,
+                                       device)
+        self.has_feed_forward = layer.feed_forward.kind != "none"
+        self.ffn_norm = self.ffn_scale = None
+        if self.has_feed_forward:
+            self.ffn_norm = build_part("norm", spec["feed_forward_norm"], weights, dtype, device)
+            self.ffn_scale = scale("feed_forward_scale")
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and type(norm) is not RmsNorm:
+                raise ConfigError("the output-norm block fuses an RMS norm with the residual "
+                                  f"sum; it has no form for {type(norm).__name__}")
+
+    def cache_needs(self):
+        return [self.mixer.cache_need()]
+
+    def streamed_weights(self):
+        return streamed_weights_of(self.mixer) + streamed_weights_of(self.feed_forward)
+
+    @property
+    def graph_safe(self) -> bool:
+        return graph_safe(self.mixer) and graph_safe(self.feed_forward)
+
+    @staticmethod
+    def _input(ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
+        if ctx.dtype == torch.float32:
+            return x                   # the sublayer only reads it; x changes after it is done
+        h = ctx.buffer("block.h", x.shape)
+        kernels.cast_rows(x, h)
+        return h
+
+    def forward(self, ctx: StepContext, call: BoundCall, x: torch.Tensor) -> None:
+        y = ctx.buffer("block.y", x.shape, torch.float32)
+        self.mixer.forward(ctx, call.for_need(0) if call.cache_entries else call,
+                           self._input(ctx, x), y, accumulate=False)
+        kernels.norm_scale_add(y, self.mixer_norm.weight, self.mixer_scale, x,
+                               self.mixer_norm.eps)
+        if self.has_feed_forward:
+            self.feed_forward.forward(ctx, self._input(ctx, x), y, accumulate=False)
+            kernels.norm_scale_add(y, self.ffn_norm.weight, self.ffn_scale, x, self.ffn_norm.eps)
+
+
 register_part("block", "pre_norm_residual", PreNormResidualBlock, replace=True)
+register_part("block", "output_norm_residual", OutputNormResidualBlock, replace=True)

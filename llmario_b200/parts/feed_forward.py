@@ -35,11 +35,31 @@ class SwiGLU:
     def streamed_weights(self):
         return [self.gate_up.weight, self.down.weight]
 
-    def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor) -> None:
+    def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        """Adds the result into ``x``; with ``accumulate=False`` ``x`` (float32) receives it."""
         rows = ctx.rows
         act = ctx.buffer("ffn.act", (rows, self.ff))
         kernels.gate_up_silu(ctx, h, self.gate_up.weight, act, self.interleaved)
-        self.down(act, x, accumulate=True)
+        self.down(act, x, accumulate=accumulate)
+
+
+class NoFeedForward:
+    """A layer without a feed-forward: no tensors, no work."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        pass
+
+    def streamed_weights(self):
+        return []
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        if not accumulate:
+            raise RuntimeError("a layer without a feed-forward has no result to hand over")
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+register_part("feed_forward", "none", NoFeedForward, replace=True)

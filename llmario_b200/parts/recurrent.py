@@ -1,0 +1,191 @@
+"""Mixers that carry a matrix state per head from token to token instead of keys and values:
+
+* ``gla``: gated linear attention with a decay per key channel,
+  ``S_t = diag(alpha_t) S_{t-1} + k_t v_t^T``, ``o_t = S_t^T q_t`` with
+  ``alpha = sigmoid(W_a2 W_a1 h + b)^(1/tau)`` and ``q`` scaled by ``key_dim^(-1/2)``; each
+  head's output is RMS-normed (one weight over the value channels, shared by the heads),
+  multiplied by ``silu(W_g h)`` and projected.
+* ``mamba2``: a state-space mixer with one decay per head,
+  ``S_t = exp(-exp(A_log) dt_t) S_{t-1} + dt_t B_t x_t^T``, ``y_t = S_t^T C_t + D x_t`` with
+  ``dt = softplus(dt + dt_bias)``; x, B and C pass a short causal convolution per channel and
+  silu first, B and C are shared by the heads of a group; ``y silu(z)`` is RMS-normed in equal
+  groups of channels and projected.
+
+Both are the same recurrence (``csrc/recurrent.cu``), told by data how the decay is made.  The
+state (and the convolution's last inputs) is 32-bit and lives in the request's fixed-size state
+slot of the cache manager, which clears a slot when a request is opened in it.  Everything
+behind the projections is computed in 32-bit.  Which rows belong to which request is read on
+the device, so steps of single tokens can be recorded and replayed.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels
+from ..cache import FixedState
+from ..config.spec import ConfigError, PartSpec
+from .base import BoundCall, StepContext, optional_tensor_of, register_part, tensor_of
+from .linear import Linear
+
+
+def step_segments(ctx: StepContext) -> Optional[torch.Tensor]:
+    """The table (first row, end row) per request slot of this step, made once per step on the
+    device; None when every row is a request of its own (the kernels then go by ``row_slot``)."""
+    if ctx.rows == len(ctx.segments):
+        return None
+    seg = ctx.shared.get("segments")
+    if seg is None:
+        seg = ctx.buffer("segments", (ctx.cache.max_requests, 2), torch.int32)
+        kernels.segment_table(ctx.row_slot, seg)
+        ctx.shared["segments"] = seg
+    return seg
+
+
+def _f32(t: torch.Tensor, device) -> torch.Tensor:
+    return t.to(device=device, dtype=torch.float32).contiguous()
+
+
+def _padded_rows(mats, hidden: int):
+    """The matrices stacked into one product, rows padded to a multiple of 16 (the 32-bit output
+    keeps rows of whole 16-byte units)."""
+    n = sum(m.shape[0] for m in mats)
+    if n % 16:
+        mats = list(mats) + [torch.zeros(16 - n % 16, hidden, dtype=mats[0].dtype,
+                                         device=mats[0].device)]
+    return Linear.stacked(mats)
+
+
+class GatedLinearAttention:
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = int(spec["hidden_size"])
+        self.heads = int(spec["num_heads"])
+        self.key_dim = int(spec["key_dim"])
+        self.value_dim = int(spec["value_dim"])
+        self.tau = float(spec["tau"])
+        self.eps = float(spec["eps"])
+        if self.tau <= 0:
+            raise ConfigError(f"gla: tau {self.tau} must be positive")
+        if self.key_dim > 256:
+            raise ConfigError(f"gla: key_dim {self.key_dim}: the recurrence keeps at most 256 key "
+                              "channels of a state column in registers")
+        t = {r: tensor_of(spec, r, weights) for r in ("q", "k", "v", "g", "a1", "a2", "o")}
+        self.rank = t["a1"].shape[0]          # the decay's low rank: the tensors' own size
+        if t["a2"].shape[1] != self.rank:
+            raise ConfigError(f"gla: the decay's two factors disagree on their rank "
+                              f"({self.rank} and {t['a2'].shape[1]})")
+        hk, hv = self.heads * self.key_dim, self.heads * self.value_dim
+        self.col_k, self.col_v, self.col_g, self.col_a = hk, 2 * hk, 2 * hk + hv, 2 * hk + 2 * hv
+        self.in_proj = _padded_rows([t["q"], t["k"], t["v"], t["g"], t["a1"]], self.hidden)
+        self.decay_proj = Linear(t["a2"], optional_tensor_of(spec, "a2_bias", weights))
+        self.o_proj = Linear(t["o"])
+        self.norm_weight = _f32(tensor_of(spec, "norm", weights), device)
+        if self.norm_weight.numel() != self.value_dim:
+            raise ConfigError("gla: the output norm has one weight per value channel of a head")
+
+    def cache_need(self):
+        return FixedState((self.heads * self.value_dim * self.key_dim,), torch.float32)
+
+    def streamed_weights(self):
+        return [self.in_proj.weight, self.decay_proj.weight, self.o_proj.weight]
+
+    def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        rows, H, K, V = ctx.rows, self.heads, self.key_dim, self.value_dim
+        state = ctx.cache.state_of(call.cache_entry)
+        if state is None:
+            raise RuntimeError(f"run-order entry {call.index}: the recurrence needs a state slot")
+        proj = ctx.buffer("gla.proj", (rows, self.in_proj.out_features), torch.float32)
+        self.in_proj(h, proj)
+        low = proj[:, self.col_a:self.col_a + self.rank]
+        if ctx.dtype != torch.float32:           # the operand of the second, low-rank product
+            low16 = ctx.buffer("gla.low", (rows, self.rank))
+            kernels.cast_rows(low, low16)
+            low = low16
+        z = ctx.buffer("gla.z", (rows, H * K), torch.float32)
+        self.decay_proj(low, z)
+        o = ctx.buffer("gla.o", (rows, H * V), torch.float32)
+        kernels.linear_recurrence(
+            proj[:, :self.col_k], proj[:, self.col_k:self.col_v], proj[:, self.col_v:self.col_g],
+            z, state, o, ctx.row_slot, step_segments(ctx), H, H, K, V,
+            kernels.DECAY_SIGMOID_POW, q_scale=K ** -0.5, exponent=1.0 / self.tau)
+        gated = ctx.buffer("gla.gated", (rows, H * V))
+        kernels.gated_group_norm(o, proj[:, self.col_g:self.col_a], self.norm_weight, gated,
+                                 group=V, eps=self.eps, gate_first=False)
+        self.o_proj(gated, x, accumulate=accumulate)
+
+
+class StateSpaceMixer:
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = int(spec["hidden_size"])
+        self.heads = int(spec["num_heads"])
+        self.head_dim = int(spec["head_dim"])
+        self.state_dim = int(spec["state_dim"])
+        self.groups = int(spec["groups"])
+        self.taps = int(spec["conv_taps"])
+        self.norm_groups = int(spec["norm_groups"])
+        self.eps = float(spec["eps"])
+        self.inner = self.heads * self.head_dim
+        if self.heads % self.groups:
+            raise ConfigError(f"mamba2: {self.heads} heads cannot share {self.groups} groups")
+        if self.inner % self.norm_groups:
+            raise ConfigError(f"mamba2: {self.inner} channels in {self.norm_groups} norm groups")
+        if self.state_dim > 256:
+            raise ConfigError(f"mamba2: state {self.state_dim}: the recurrence keeps at most 256 "
+                              "state rows of a column in registers")
+        if self.taps < 1:
+            raise ConfigError("mamba2: the convolution has at least one tap")
+        gn = self.groups * self.state_dim
+        self.conv_channels = self.inner + 2 * gn
+        self.col_x, self.col_dt = self.inner, 2 * self.inner + 2 * gn
+        self.in_proj = _padded_rows([tensor_of(spec, "in", weights)], self.hidden)
+        self.o_proj = Linear(tensor_of(spec, "o", weights))
+        self.conv_weight = _f32(tensor_of(spec, "conv", weights), device)
+        bias = optional_tensor_of(spec, "conv_bias", weights)
+        self.conv_bias = None if bias is None else _f32(bias, device)
+        self.step_bias = _f32(tensor_of(spec, "dt_bias", weights), device)
+        self.rate_log = _f32(tensor_of(spec, "A_log", weights), device)
+        self.skip = _f32(tensor_of(spec, "D", weights), device)
+        self.norm_weight = _f32(tensor_of(spec, "norm", weights), device)
+        self.state_floats = self.heads * self.head_dim * self.state_dim
+
+    def cache_need(self):
+        """The matrix state of every head, then every convolved channel's last taps - 1 inputs."""
+        return FixedState((self.state_floats + self.conv_channels * (self.taps - 1),),
+                          torch.float32)
+
+    def streamed_weights(self):
+        return [self.in_proj.weight, self.o_proj.weight]
+
+    def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        rows, H, P, N, G = ctx.rows, self.heads, self.head_dim, self.state_dim, self.groups
+        state = ctx.cache.state_of(call.cache_entry)
+        if state is None:
+            raise RuntimeError(f"run-order entry {call.index}: the recurrence needs a state slot")
+        seg = step_segments(ctx)
+        proj = ctx.buffer("ssm.proj", (rows, self.in_proj.out_features), torch.float32)
+        self.in_proj(h, proj)                    # [z | x | B | C | dt]
+        xbc = ctx.buffer("ssm.conv", (rows, self.conv_channels), torch.float32)
+        kernels.causal_conv_silu(proj[:, self.col_x:self.col_dt], self.conv_weight, self.conv_bias,
+                                 state[:, self.state_floats:], xbc, ctx.row_slot, seg)
+        o = ctx.buffer("ssm.o", (rows, self.inner), torch.float32)
+        kernels.linear_recurrence(
+            xbc[:, self.inner + G * N:], xbc[:, self.inner:self.inner + G * N], xbc[:, :self.inner],
+            proj[:, self.col_dt:self.col_dt + H], state, o, ctx.row_slot, seg, H, G, N, P,
+            kernels.DECAY_RATE_STEP, rate_log=self.rate_log, step_bias=self.step_bias)
+        gated = ctx.buffer("ssm.gated", (rows, self.inner))
+        kernels.gated_group_norm(o, proj[:, :self.inner], self.norm_weight, gated,
+                                 group=self.inner // self.norm_groups, eps=self.eps,
+                                 gate_first=True, skip=self.skip, skip_input=xbc[:, :self.inner],
+                                 head=P)
+        self.o_proj(gated, x, accumulate=accumulate)
+
+
+register_part("mixer", "gla", GatedLinearAttention, replace=True)
+register_part("mixer", "mamba2", StateSpaceMixer, replace=True)

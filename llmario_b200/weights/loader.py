@@ -82,12 +82,22 @@ def _target_dtype(stored: torch.dtype, mode: torch.dtype) -> torch.dtype:
     return torch.int32
 
 
+FREE_DIM_DEFAULT = 16     # what a random model takes for a size that only the files decide
+
+
+def shape_matches(got: Tuple[int, ...], want: Tuple[Optional[int], ...]) -> bool:
+    """Whether a stored shape is the one a part asks for; a size the part gives as None is
+    decided by the file (a low rank that no configuration key names, for instance)."""
+    return len(got) == len(want) and all(w is None or g == w for g, w in zip(got, want))
+
+
 def check_tensors(spec: ModelSpec, shapes: Dict[str, Tuple[int, ...]], where: str = "") -> None:
     want = expected_tensors(spec)
     ignore = set(optional_tensors(spec))
     missing = [n for n in want if n not in shapes]
     unexpected = sorted(n for n in shapes if n not in want and n not in ignore)
-    wrong = [(n, shapes[n], want[n]) for n in want if n in shapes and tuple(shapes[n]) != want[n]]
+    wrong = [(n, shapes[n], want[n]) for n in want if n in shapes
+             and not shape_matches(tuple(shapes[n]), want[n])]
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong, where)
 
@@ -127,6 +137,7 @@ def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype,
     device = torch.device(device)
     for name, shape in expected_tensors(spec).items():
         key = tensor_key(seed, name)
+        shape = tuple(FREE_DIM_DEFAULT if d is None else d for d in shape)
         mean, std = (1.0, gain_std) if len(shape) == 1 else (0.0, matrix_std)
         t = torch.empty(shape, dtype=dtype, device=device)
         if device.type == "cuda":
