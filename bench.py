@@ -393,7 +393,9 @@ def main() -> int:
                          "(default 1)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="qwen3-8b")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "vunasun"])
+    ap.add_argument("--sizes", default="0.6b,8b",
+                    help="vunasun: the Qwen3 presets whose sizes both models take")
     ap.add_argument("--layers", type=int, default=None, help="build fewer layers (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
@@ -429,6 +431,8 @@ def main() -> int:
     from llmario_b200.engine.engine import Engine
 
     pk = peaks()
+    if args.workload == "vunasun":
+        return vunasun_workload(args)
     cfg = preset_config(args.model, args.layers)
     full_layers = _full_layers(args.model)
     model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
@@ -443,6 +447,38 @@ def main() -> int:
         return decode_workload(args, cfg, full_layers, model, pk, clocks)
     finally:
         clocks.stop()
+
+
+def vunasun_workload(args) -> int:
+    """Prompt and decode rates of Vunasun models with random weights beside Qwen3 models of
+    the same width, feed-forward width, heads and number of layers (``--layers``, default 8;
+    ``--sizes``), and the design's own kernels one by one against the copy rate."""
+    from llmario_b200.benchmarks import vunasun as V
+
+    clocks = ClockSampler()
+    clocks.start()
+    try:
+        steps = 64 if args.steps is None else args.steps
+        warmup = max(3, 24 if args.warmup is None else args.warmup)
+        rec = V.compare([x for x in args.sizes.split(",") if x], args.layers or 8, batch=args.batch,
+                        prompt_len=args.prompt_len, prefill_tokens=args.prefill_tokens, steps=steps,
+                        warmup=warmup, page_size=64)
+        rec["kernels"] = V.kernel_table()
+    finally:
+        clocks.stop()
+    first = rec["sizes"][next(iter(rec["sizes"]))]
+    line = {"metric": "decode tokens per second of a Vunasun model beside Qwen3 at equal sizes",
+            "value": first["vunasun"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": first["vunasun"]["decode_ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (random weights, uniform random token ids)",
+            "config": {"workload": "vunasun", "layers": rec["layers"], "batch": rec["batch"],
+                       "prompt_len": rec["prompt_len"], "prefill_tokens": rec["prefill_tokens"],
+                       "l2": "weights larger than L2 (steps); flushed (kernels)"},
+            "clocks": clocks.summary(), "sizes": rec["sizes"], "kernels": rec["kernels"],
+            "peaks": rec["peaks"]}
+    print(json.dumps(line))
+    return 0
 
 
 def decode_workload(args, cfg, full_layers, model, pk, clocks):

@@ -5,7 +5,7 @@
 // Keys are visited in tiles of 32 aligned to absolute positions, each lane scoring one key, so
 // the order of every sum depends only on positions: the result for a row is the same however the
 // tokens were cut into steps, whatever else is in the batch and whichever pages hold the keys.
-// Any head size up to 256 that is a multiple of 8; any number of heads and groups.
+// Any head size up to 256 (multiples of 8 are read in wide pieces); any number of heads and groups.
 #include "common.cuh"
 
 namespace {
@@ -34,7 +34,8 @@ template <> struct Vec8<bf16> {
   }
 };
 
-template <typename T>
+// VEC: the head size is a multiple of 8, so a key row is read in 16-byte (32-byte) pieces.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
     const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ k_cache,
     const T* __restrict__ v_cache, long long page_stride, const int* __restrict__ block_table,
@@ -70,11 +71,15 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
       off = (long long)page * page_stride + ((long long)kvh * page_size + p % page_size) * hd;
       const T* kr = k_cache + off;
       float d = 0.f;
-      for (int i = 0; i < hd; i += 8) {
-        Vec8<T> kv;
-        kv.load(kr + i);
+      if (VEC) {
+        for (int i = 0; i < hd; i += 8) {
+          Vec8<T> kv;
+          kv.load(kr + i);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) d = fmaf(qs[i + j], kv.v[j], d);
+          for (int j = 0; j < 8; ++j) d = fmaf(qs[i + j], kv.v[j], d);
+        }
+      } else {
+        for (int i = 0; i < hd; ++i) d = fmaf(qs[i], to_f32(kr[i]), d);
       }
       s = d * scale;
     }
@@ -114,18 +119,22 @@ LLM_EXPORT int llm_attention_generic(const void* q, void* out, const void* k_cac
                                      const int* row_pos, int rows, int Hq, int Hkv, int hd,
                                      int page_size, float scale, int window, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (hd > MAX_HD || hd % 8 != 0 || Hkv <= 0 || Hq % Hkv != 0) return LLM_ERR_UNSUPPORTED;
+  if (hd > MAX_HD || hd <= 0 || Hkv <= 0 || Hq % Hkv != 0) return LLM_ERR_UNSUPPORTED;
+  const bool vec = hd % 8 == 0 && (page_stride % 8) == 0 &&
+                   (((uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0;
   const long long items = (long long)rows * Hq;
   const int blocks = (int)((items + WARPS - 1) / WARPS);
-  if (dtype == LLM_F32)
-    attention_generic_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
-        (const float*)q, (float*)out, (const float*)k_cache, (const float*)v_cache, page_stride,
-        block_table, table_stride, row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window);
-  else if (dtype == LLM_BF16)
-    attention_generic_kernel<bf16><<<blocks, WARPS * 32, 0, stream>>>(
-        (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, page_stride,
-        block_table, table_stride, row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window);
-  else
+#define GENERIC(T, V)                                                                               \
+  attention_generic_kernel<T, V><<<blocks, WARPS * 32, 0, stream>>>(                                \
+      (const T*)q, (T*)out, (const T*)k_cache, (const T*)v_cache, page_stride, block_table,         \
+      table_stride, row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window)
+  if (dtype == LLM_F32) {
+    if (vec) GENERIC(float, true); else GENERIC(float, false);
+  } else if (dtype == LLM_BF16) {
+    if (vec) GENERIC(bf16, true); else GENERIC(bf16, false);
+  } else {
     return LLM_ERR_UNSUPPORTED;
+  }
+#undef GENERIC
   return launch_status();
 }

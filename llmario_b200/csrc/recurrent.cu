@@ -200,7 +200,7 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ src, int src_s
                                         int single, float* __restrict__ out, int out_stride, int C, int taps) {
   pdl_trigger();
   pdl_wait();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x, r = blockIdx.x;
   if (c >= C) return;
   const int slot = row_slot[r];
   const int before = single ? 0 : r - seg[slot].x;       // rows of the request in this step before r
@@ -220,13 +220,13 @@ __global__ void conv_history_kernel(const float* __restrict__ src, int src_strid
                                     const int2* __restrict__ seg, int single, int C, int taps) {
   pdl_trigger();
   pdl_wait();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
   int slot, first, end;
   if (single) {
-    first = blockIdx.y, end = first + 1, slot = row_slot[first];
+    first = blockIdx.x, end = first + 1, slot = row_slot[first];
   } else {
-    slot = blockIdx.y;
+    slot = blockIdx.x;
     const int2 s = seg[slot];
     first = s.x, end = s.y;
   }
@@ -320,10 +320,10 @@ LLM_EXPORT int llm_causal_conv_silu(const float* src, int src_stride, const floa
                                     int taps, cudaStream_t stream) {
   if (rows <= 0 || C <= 0) return 0;
   if (taps < 1 || (!single && !seg)) return LLM_ERR_ARGUMENT;
-  int rc = launch_pdl(causal_conv_silu_kernel, dim3((C + 127) / 128, rows), 128, 0, stream, src, src_stride, w, b,
+  int rc = launch_pdl(causal_conv_silu_kernel, dim3(rows, (C + 127) / 128), 128, 0, stream, src, src_stride, w, b,
                       (const float*)hist, hist_stride, row_slot, (const int2*)seg, single, out, out_stride, C, taps);
   if (rc != 0 || taps == 1) return rc;
-  return launch_pdl(conv_history_kernel, dim3((C + 127) / 128, single ? rows : n_slots), 128, 0, stream, src,
+  return launch_pdl(conv_history_kernel, dim3(single ? rows : n_slots, (C + 127) / 128), 128, 0, stream, src,
                     src_stride, hist, hist_stride, row_slot, (const int2*)seg, single, C, taps);
 }
 

@@ -562,7 +562,12 @@ def token_tile(rows: int) -> int:
     return 256 if rows >= 512 else 128
 
 
-def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> bool:
+    """Whether the tensor-core product takes these operands: 16-bit, and every row of every
+    operand (the output's too: it leaves through a TMA store) starts on a 16-byte boundary."""
+    if out is not None and ((out.stride(0) * out.element_size()) % 16 or out.data_ptr() % 16
+                            or out.stride(1) != 1):
+        return False
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1
             and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -645,7 +650,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
     CUDA-core kernels for everything else (32-bit operands, unaligned sizes).
     ``out_is_zero``: the caller guarantees that ``out`` holds zeros, so a split-K product need
     not clear it first."""
-    if _tc_ok(a, w):
+    if _tc_ok(a, w, out):
         rows, k = a.shape
         n = w.shape[0]
         splits = k_splits(rows, n, k) if out.dtype == torch.float32 else 1
@@ -668,11 +673,11 @@ def gate_up_silu(ctx, h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tenso
     gate rows then up rows, or (``interleaved``) alternating blocks of 16 gate and 16 up rows."""
     rows, ff = act.shape
     if interleaved:
-        if not _tc_ok(h, w_gate_up):
+        if not _tc_ok(h, w_gate_up, act):
             raise KernelError("interleaved gate/up weights need the tensor-core product")
         gemm_tcgen05(h, w_gate_up, act, 3, ff)
         return
-    if _tc_ok(h, w_gate_up):
+    if _tc_ok(h, w_gate_up, act):
         gemm_tcgen05(h, w_gate_up, act, 2, ff)
         return
     if _gemv_ok(h, w_gate_up):
@@ -689,9 +694,9 @@ ATTENTION_MAX_HEAD_DIM = 256      # MAX_HD of attention_generic.cu, the kernel o
 
 def attention_refusal(num_heads: int, num_kv_heads: int, head_dim: int) -> Optional[str]:
     """Why no attention kernel of this library takes these sizes, or None when one does (the
-    generic kernel takes every head size that is a multiple of 8 up to 256 and every group)."""
-    if head_dim <= 0 or head_dim % 8 != 0 or head_dim > ATTENTION_MAX_HEAD_DIM:
-        return (f"head_dim {head_dim}: the attention kernels take multiples of 8 up to "
+    generic kernel takes every head size up to 256 and every group)."""
+    if head_dim <= 0 or head_dim > ATTENTION_MAX_HEAD_DIM:
+        return (f"head_dim {head_dim}: the attention kernels take head sizes up to "
                 f"{ATTENTION_MAX_HEAD_DIM}")
     if num_kv_heads <= 0 or num_heads % num_kv_heads != 0:
         return f"{num_heads} query heads cannot be shared among {num_kv_heads} KV heads"
