@@ -185,17 +185,21 @@ def kernel_table(width: int = 4096, tokens: int = 2048, batch: int = 64) -> List
                     else torch.zeros(rows, dtype=torch.int32, device=dev))
         seg = None
         if not single:
-            seg = torch.empty(slots, 2, dtype=torch.int32, device=dev)
+            seg = torch.empty(slots, 3, dtype=torch.int32, device=dev)
             kernels.segment_table(row_slot, seg)
         # gated linear attention: heads of 128 key and 256 value channels
         H, K, V = max(1, width // 256), 128, 256
         proj = f32(rows, 2 * H * K + 2 * H * V + 64) * 0.1
-        z = f32(rows, H * K) + 2
+        z = torch.sigmoid(f32(rows, H * K) + 2)
+        zb = f32(H * K)
+        us = _time(lambda: kernels.bias_sigmoid_pow(z, zb, 1 / 16), flush=flush)
+        rec(f"bias_sigmoid_pow ({label})", us, rows * H * K * 8)
+        z = torch.sigmoid(f32(rows, H * K) + 2)
         state = torch.zeros(slots, H * V * K, dtype=torch.float32, device=dev)
         o = torch.empty(rows, H * V, dtype=torch.float32, device=dev)
         us = _time(lambda: kernels.linear_recurrence(
             proj[:, :H * K], proj[:, H * K:2 * H * K], proj[:, 2 * H * K:2 * H * K + H * V], z, state, o,
-            row_slot, seg, H, H, K, V, kernels.DECAY_SIGMOID_POW, q_scale=K ** -0.5, exponent=1 / 16), flush=flush)
+            row_slot, seg, H, H, K, V, kernels.DECAY_VECTOR, q_scale=K ** -0.5, n_requests=1), flush=flush)
         live = rows if single else 1
         moved = rows * (3 * H * K + 2 * H * V) * 4 + 2 * live * H * V * K * 4
         rec(f"linear_recurrence gla ({label})", us, moved,
@@ -219,7 +223,8 @@ def kernel_table(width: int = 4096, tokens: int = 2048, batch: int = 64) -> List
         a_log, dtb = f32(H2) * 0.1, f32(H2) * 0.1
         us = _time(lambda: kernels.linear_recurrence(
             xbc[:, inner + N:], xbc[:, inner:inner + N], xbc[:, :inner], proj2[:, 2 * inner + 2 * N:], st2, o2,
-            row_slot, seg, H2, G, N, P, kernels.DECAY_RATE_STEP, rate_log=a_log, step_bias=dtb), flush=flush)
+            row_slot, seg, H2, G, N, P, kernels.DECAY_RATE_STEP, rate_log=a_log, step_bias=dtb, n_requests=1),
+            flush=flush)
         moved = rows * (2 * N + 2 * inner + H2) * 4 + 2 * live * H2 * P * N * 4
         rec(f"linear_recurrence mamba2 ({label})", us, moved)
         g2 = torch.empty(rows, inner, dtype=torch.bfloat16, device=dev)
@@ -246,10 +251,14 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--kernels", action="store_true", help="time the design's kernels one by one")
+    ap.add_argument("--only-kernels", action="store_true", help="leave the whole models out")
+    ap.add_argument("--width", type=int, default=4096, help="--kernels: the models' width")
+    ap.add_argument("--tokens", type=int, default=2048, help="--kernels: tokens of the prompt")
     a = ap.parse_args(argv)
-    out = compare([s for s in a.sizes.split(",") if s], a.layers, batch=a.batch, steps=a.steps)
-    if a.kernels:
-        out["kernels"] = kernel_table()
+    out = {} if a.only_kernels else compare([s for s in a.sizes.split(",") if s], a.layers,
+                                            batch=a.batch, steps=a.steps)
+    if a.kernels or a.only_kernels:
+        out["kernels"] = kernel_table(a.width, a.tokens)
     print(json.dumps(out))
     return 0
 

@@ -370,10 +370,44 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, long long x_stride
   }
 }
 
+// The same, four values per thread: rows of whole 16-byte units on both sides.
+template <typename TOut>
+__global__ void cast_rows_vec_kernel(const float* __restrict__ x, long long x_stride, TOut* __restrict__ out,
+                                     long long out_stride, int rows, int cols4) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = (long long)rows * cols4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols4, c = (i - r * cols4) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(x + r * x_stride + c);
+    TOut* dst = out + r * out_stride + c;
+    if (sizeof(TOut) == 4) {
+      *reinterpret_cast<float4*>(dst) = v;
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(dst) = packed;
+    }
+  }
+}
+
 LLM_EXPORT int llm_cast_rows(const float* x, long long x_stride, void* out, int out_dtype,
                              long long out_stride, int rows, int cols, cudaStream_t stream) {
   const long long total = (long long)rows * cols;
   if (total <= 0) return 0;
+  if (cols % 4 == 0 && x_stride % 4 == 0 && out_stride % 4 == 0 &&
+      (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+    const long long t4 = total / 4;
+    const int vb = (int)((t4 + 255) / 256 < 2368 ? (t4 + 255) / 256 : 2368);
+    if (out_dtype == LLM_F32)
+      return launch_pdl(cast_rows_vec_kernel<float>, vb, 256, 0, stream, x, x_stride, (float*)out, out_stride, rows, cols / 4);
+    if (out_dtype == LLM_BF16)
+      return launch_pdl(cast_rows_vec_kernel<bf16>, vb, 256, 0, stream, x, x_stride, (bf16*)out, out_stride, rows, cols / 4);
+    return LLM_ERR_UNSUPPORTED;
+  }
   const int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
   if (out_dtype == LLM_F32)
     return launch_pdl(cast_rows_kernel<float>, blocks, 256, 0, stream, x, x_stride, (float*)out, out_stride, rows, cols);

@@ -14,25 +14,33 @@
 //
 // Which rows of a step belong to which request is read on the device: either every row is a
 // request of its own (`single`: slot = row_slot[row]), or a table of (first row, end row) per
-// request slot made by llm_segment_table from row_slot.  No host data is involved, so steps of
+// request slot made by llm_segment_table from row_slot (with the list of the slots that have rows).  No host data is involved, so steps of
 // single tokens can be recorded and replayed.
 #include "common.cuh"
 
 namespace {
 
-// seg[s] = (first row, row after the last) of the rows whose request slot is s; (0, 0): none.
-// The rows of a request are consecutive in a step.
-__global__ void segment_table_kernel(const int* __restrict__ row_slot, int rows, int2* __restrict__ seg,
+// The table has three integers per request slot s: (first row, row after the last) of the rows
+// whose request slot is s, (0, 0) for none; and, as the third of entry i, the slot of the i-th
+// request that has rows in this step (in no particular order), so that a kernel can run one
+// block per request of the step instead of one per slot.  The rows of a request are consecutive.
+constexpr int SEG = 3;
+__global__ void segment_table_kernel(const int* __restrict__ row_slot, int rows, int* __restrict__ seg,
                                      int n_slots) {
+  __shared__ int count;
   pdl_trigger();
   pdl_wait();
-  for (int s = threadIdx.x; s < n_slots; s += blockDim.x) seg[s] = make_int2(0, 0);
+  if (threadIdx.x == 0) count = 0;
+  for (int s = threadIdx.x; s < n_slots; s += blockDim.x) seg[SEG * s] = seg[SEG * s + 1] = 0, seg[SEG * s + 2] = -1;
   __syncthreads();
   for (int r = threadIdx.x; r < rows; r += blockDim.x) {
     const int s = row_slot[r];
     if (s < 0 || s >= n_slots) continue;
-    if (r == 0 || row_slot[r - 1] != s) seg[s].x = r;
-    if (r == rows - 1 || row_slot[r + 1] != s) seg[s].y = r + 1;
+    if (r == 0 || row_slot[r - 1] != s) {
+      seg[SEG * s] = r;
+      seg[SEG * atomicAdd(&count, 1) + 2] = s;
+    }
+    if (r == rows - 1 || row_slot[r + 1] != s) seg[SEG * s + 1] = r + 1;
   }
 }
 
@@ -53,29 +61,46 @@ struct ScanArgs {
   const float* d; int d_stride;          // the decay's argument (see DecayKind)
   const float* p0; const float* p1;      // per-head constants of DECAY_RATE_STEP
   float c;                               // the exponent of DECAY_SIGMOID_POW
-  float q_scale;                         // q is multiplied by it
+  float q_scale;                         // q is multiplied by it (applied to the head's output: the same product)
   float* state; long long state_stride;  // state[slot * state_stride + ((h * V) + j) * K + i]
   float* out; int out_stride;            // out[row * out_stride + h * V + j]
-  const int2* seg; const int* row_slot;
+  const int* seg; const int* row_slot;
   int single, H, G, K, V, kind;
 };
 
 constexpr int SCAN_THREADS = 128;
-constexpr int SCAN_COLS = 16;      // value channels of a block: four to a warp, eight lanes to a channel
 
-// A block owns 16 value channels of one head of one request and walks the request's tokens of
-// the step in order.  Lane (c, i) of a warp holds, of column c, the state rows 4 (i + 8 n) + e
-// (n < KR4, e < 4) in registers; the token's q, k and decay are staged in shared memory for a
-// chunk of tokens at a time and read as 16-byte values that the four columns of a warp share.
-template <int KR4, bool VEC>
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// A block owns a tile of value channels of one head of one request and walks the request's
+// tokens of the step in order.  L lanes share a group of four columns: lane i of the group holds,
+// of each of the four, the state rows 4 (i + L n) + e (n < NF, e < 4) in registers, so one
+// 16-byte read of q, k and the decay from shared memory serves sixteen state elements.  Per
+// token a lane has four partial sums (one per column); they are summed over the L lanes by a
+// butterfly whose first two steps each hand half of the columns to the partner, six shuffles
+// for 32 lanes.  The tokens' q, k and decay arguments come into shared memory a chunk of tokens
+// at a time by asynchronous copies, two chunks in flight: while one chunk is walked the next is
+// on its way.
+template <int L, int NF, bool VEC>
 __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const ScanArgs a) {
-  constexpr int KP = 32 * KR4;                 // key channels, padded
-  constexpr int TC = KR4 >= 8 ? 8 : 16;        // tokens of a chunk
-  __shared__ float4 q_s[TC][KP / 4];
-  __shared__ float4 k_s[TC][KP / 4];
-  __shared__ float4 a_s[VEC ? TC : 1][KP / 4];
-  __shared__ float v_s[TC][SCAN_COLS];
-  __shared__ float a1_s[TC];
+  constexpr int KP = 4 * L * NF;                            // key channels, padded
+  constexpr int GROUPS = 32 / L;                            // column groups of a warp
+  constexpr int COLS = 4 * GROUPS * (SCAN_THREADS / 32);    // value channels of a block
+  constexpr int TC = KP >= 256 ? 4 : (KP >= 128 ? 8 : 16);  // tokens of a chunk
+  __shared__ __align__(16) float q_s[2][TC][KP];
+  __shared__ __align__(16) float k_s[2][TC][KP];
+  __shared__ __align__(16) float a_s[2][VEC ? TC : 1][VEC ? KP : 4];
+  __shared__ __align__(16) float v_s[2][TC][COLS];
+  __shared__ float d_s[2][TC];          // scalar decay: its argument, then the decay itself
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -83,109 +108,188 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
   if (a.single) {
     first = blockIdx.x, end = first + 1, slot = a.row_slot[first];
   } else {
-    slot = blockIdx.x;
-    const int2 s = a.seg[slot];
-    first = s.x, end = s.y;
+    slot = a.seg[SEG * blockIdx.x + 2];
+    if (slot < 0) return;
+    first = a.seg[SEG * slot], end = a.seg[SEG * slot + 1];
   }
   if (end <= first) return;
   const int K = a.K, V = a.V, g = h / (a.H / a.G);
-  const int j0 = blockIdx.z * SCAN_COLS;
-  const int col = warp * 4 + (lane >> 3), j = j0 + col, ki = lane & 7;
-  const bool live = j < V;
-  float* srow = a.state + (size_t)slot * a.state_stride + ((size_t)h * V + (live ? j : 0)) * K;
-  const bool k4 = (K & 3) == 0 && ((uintptr_t)srow & 15) == 0;
+  const int j0 = blockIdx.z * COLS;
+  const int li = lane % L;
+  const int c0 = (warp * GROUPS + lane / L) * 4, jc = j0 + c0;     // this lane's four columns
+  float* sbase = a.state + (size_t)slot * a.state_stride + (size_t)h * V * K;
+  const bool k4 = (K & 3) == 0 && ((uintptr_t)sbase & 15) == 0;
 
-  float s[KR4][4];
-#pragma unroll
-  for (int n = 0; n < KR4; ++n) {
-    const int i0 = 4 * (ki + 8 * n);
-    if (live && k4 && i0 + 3 < K) {
-      const float4 t = *reinterpret_cast<const float4*>(srow + i0);
-      s[n][0] = t.x, s[n][1] = t.y, s[n][2] = t.z, s[n][3] = t.w;
+  // key channels beyond K: they hold nothing and must stay that way
+  for (int idx = tid; idx < 2 * TC * (KP - K); idx += SCAN_THREADS) {
+    const int st = idx / (TC * (KP - K)), rem = idx - st * TC * (KP - K);
+    const int tt = rem / (KP - K), i = K + rem - tt * (KP - K);
+    q_s[st][tt][i] = 0.f;
+    k_s[st][tt][i] = 0.f;
+    if (VEC) a_s[st][tt][i] = 1.f;
+  }
+  // whether whole 16-byte pieces can be copied: every row of q, k and the decay's argument
+  // starts on a 16-byte boundary
+  const bool wide = (K & 3) == 0 && !((a.q_stride | a.k_stride | (VEC ? a.d_stride : 0)) & 3) &&
+                    !(((uintptr_t)(a.q + g * K) | (uintptr_t)(a.k + g * K) |
+                       (VEC ? (uintptr_t)(a.d + h * K) : 0)) & 15);
+  auto fetch = [&](int st, int t0) {
+    const int n_tok = min(TC, end - t0);
+    if (wide) {
+      const int k4n = K >> 2;
+      for (int idx = tid; idx < n_tok * k4n; idx += SCAN_THREADS) {
+        const int tt = idx / k4n, i = (idx - tt * k4n) << 2;
+        const size_t row = (size_t)(t0 + tt);
+        cp_async16(&q_s[st][tt][i], a.q + row * a.q_stride + g * K + i);
+        cp_async16(&k_s[st][tt][i], a.k + row * a.k_stride + g * K + i);
+        if (VEC) cp_async16(&a_s[st][tt][i], a.d + row * a.d_stride + h * K + i);
+      }
     } else {
+      for (int idx = tid; idx < n_tok * K; idx += SCAN_THREADS) {
+        const int tt = idx / K, i = idx - tt * K;
+        const size_t row = (size_t)(t0 + tt);
+        cp_async4(&q_s[st][tt][i], a.q + row * a.q_stride + g * K + i);
+        cp_async4(&k_s[st][tt][i], a.k + row * a.k_stride + g * K + i);
+        if (VEC) cp_async4(&a_s[st][tt][i], a.d + row * a.d_stride + h * K + i);
+      }
+    }
+    for (int idx = tid; idx < n_tok * COLS; idx += SCAN_THREADS) {
+      const int tt = idx / COLS, cc = idx - tt * COLS;
+      if (j0 + cc < V) cp_async4(&v_s[st][tt][cc], a.v + (size_t)(t0 + tt) * a.v_stride + h * V + j0 + cc);
+      else v_s[st][tt][cc] = 0.f;
+    }
+    if (!VEC)
+      for (int tt = tid; tt < n_tok; tt += SCAN_THREADS)
+        cp_async4(&d_s[st][tt], a.d + (size_t)(t0 + tt) * a.d_stride + h);
+    cp_async_commit();
+  };
+
+  fetch(0, first);
+  float s[NF][4][4];       // [n][row e][column c]
 #pragma unroll
-      for (int e = 0; e < 4; ++e) s[n][e] = (live && i0 + e < K) ? srow[i0 + e] : 0.f;
+  for (int c = 0; c < 4; ++c) {
+    const bool live = jc + c < V;
+    const float* srow = sbase + (size_t)(live ? jc + c : 0) * K;
+#pragma unroll
+    for (int n = 0; n < NF; ++n) {
+      const int i0 = 4 * (li + L * n);
+      if (live && k4 && i0 + 3 < K) {
+        const float4 t = *reinterpret_cast<const float4*>(srow + i0);
+        s[n][0][c] = t.x, s[n][1][c] = t.y, s[n][2][c] = t.z, s[n][3][c] = t.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[n][e][c] = (live && i0 + e < K) ? srow[i0 + e] : 0.f;
+      }
     }
   }
 
   const float rate = a.kind == DECAY_RATE_STEP ? expf(a.p0[h]) : 0.f;
   const float bias = a.kind == DECAY_RATE_STEP ? a.p1[h] : 0.f;
-  for (int t0 = first; t0 < end; t0 += TC) {
+  const float q_scale = a.q_scale;
+  const bool up1 = (li & (L / 2)) != 0, up2 = (li & (L / 4)) != 0;
+  const int my_col = jc + 2 * (up1 ? 1 : 0) + (up2 ? 1 : 0);
+  const bool writer = (li & (L / 4 - 1)) == 0 && my_col < V;
+  int st = 0;
+  for (int t0 = first; t0 < end; t0 += TC, st ^= 1) {
     const int n_tok = min(TC, end - t0);
-    __syncthreads();
-    // ---- stage the chunk: q (scaled), k, the decay, and this block's columns of v
-    for (int idx = tid; idx < n_tok * KP; idx += SCAN_THREADS) {
-      const int tt = idx / KP, i = idx - tt * KP;
-      const size_t row = (size_t)(t0 + tt);
-      const bool in = i < K;
-      reinterpret_cast<float*>(&q_s[tt][0])[i] = in ? a.q[row * a.q_stride + g * K + i] * a.q_scale : 0.f;
-      reinterpret_cast<float*>(&k_s[tt][0])[i] = in ? a.k[row * a.k_stride + g * K + i] : 0.f;
-      if (VEC) {
-        float dec = 1.f;
-        if (in) {
-          const float d = a.d[row * a.d_stride + h * K + i];
-          // sigmoid(d)^c = exp(c * log sigmoid(d)), log sigmoid(d) = -softplus(-d)
-          dec = a.kind == DECAY_SIGMOID_POW ? expf(-a.c * softplus_f(-d)) : d;
-        }
-        reinterpret_cast<float*>(&a_s[tt][0])[i] = dec;
-      }
+    if (t0 + TC < end) {
+      fetch(st ^ 1, t0 + TC);       // (its stage was walked two chunks ago; a barrier lies between)
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-    for (int idx = tid; idx < n_tok * SCAN_COLS; idx += SCAN_THREADS) {
-      const int tt = idx / SCAN_COLS, cc = idx - tt * SCAN_COLS;
-      const size_t row = (size_t)(t0 + tt);
-      float val = j0 + cc < V ? a.v[row * a.v_stride + h * V + j0 + cc] : 0.f;
-      if (!VEC) {
-        const float step = softplus_f(a.d[row * a.d_stride + h] + bias);
-        val *= step;
-        if (cc == 0) a1_s[tt] = expf(-rate * step);
+    __syncthreads();
+    // ---- the decay from its argument, once per token
+    if (VEC) {
+      if (a.kind == DECAY_SIGMOID_POW)
+        for (int idx = tid; idx < n_tok * K; idx += SCAN_THREADS) {
+          const int tt = idx / K, i = idx - tt * K;
+          // sigmoid(d)^c = exp(c * log sigmoid(d)), log sigmoid(d) = -softplus(-d)
+          a_s[st][tt][i] = expf(-a.c * softplus_f(-a_s[st][tt][i]));
+        }
+    } else {
+      for (int idx = tid; idx < n_tok * COLS; idx += SCAN_THREADS) {
+        const int tt = idx / COLS, cc = idx - tt * COLS;
+        v_s[st][tt][cc] *= softplus_f(d_s[st][tt] + bias);
       }
-      v_s[tt][cc] = val;
+      __syncthreads();
+      for (int tt = tid; tt < n_tok; tt += SCAN_THREADS)
+        d_s[st][tt] = expf(-rate * softplus_f(d_s[st][tt] + bias));
     }
     __syncthreads();
     // ---- the tokens of the chunk, one after the other
+#pragma unroll 4
     for (int tt = 0; tt < n_tok; ++tt) {
-      const float vv = v_s[tt][col];
-      const float a1 = VEC ? 1.f : a1_s[tt];
-      float acc = 0.f;
+      const float4 vv = *reinterpret_cast<const float4*>(&v_s[st][tt][c0]);
+      const float a1 = VEC ? 1.f : d_s[st][tt];
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int n = 0; n < KR4; ++n) {
-        const float4 qq = q_s[tt][ki + 8 * n], kk = k_s[tt][ki + 8 * n];
+      for (int n = 0; n < NF; ++n) {
+        const float4 qq = *reinterpret_cast<const float4*>(&q_s[st][tt][4 * (li + L * n)]);
+        const float4 kk = *reinterpret_cast<const float4*>(&k_s[st][tt][4 * (li + L * n)]);
         float4 aa = make_float4(a1, a1, a1, a1);
-        if (VEC) aa = a_s[tt][ki + 8 * n];
-        s[n][0] = fmaf(aa.x, s[n][0], kk.x * vv);
-        s[n][1] = fmaf(aa.y, s[n][1], kk.y * vv);
-        s[n][2] = fmaf(aa.z, s[n][2], kk.z * vv);
-        s[n][3] = fmaf(aa.w, s[n][3], kk.w * vv);
-        acc = fmaf(s[n][0], qq.x, acc);
-        acc = fmaf(s[n][1], qq.y, acc);
-        acc = fmaf(s[n][2], qq.z, acc);
-        acc = fmaf(s[n][3], qq.w, acc);
+        if (VEC) aa = *reinterpret_cast<const float4*>(&a_s[st][tt][4 * (li + L * n)]);
+        const float qe[4] = {qq.x, qq.y, qq.z, qq.w}, ke[4] = {kk.x, kk.y, kk.z, kk.w};
+        const float ae[4] = {aa.x, aa.y, aa.z, aa.w}, ve[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            s[n][e][c] = fmaf(ae[e], s[n][e][c], ke[e] * ve[c]);
+            acc[c] = fmaf(s[n][e][c], qe[e], acc[c]);
+          }
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (ki == 0 && live) a.out[(size_t)(t0 + tt) * a.out_stride + h * V + j] = acc;
+      // sum over the L lanes of the group: hand two columns to the partner, then one, then a
+      // plain butterfly over what is left
+      const float r0 = __shfl_xor_sync(0xffffffffu, up1 ? acc[0] : acc[2], L / 2);
+      const float r1 = __shfl_xor_sync(0xffffffffu, up1 ? acc[1] : acc[3], L / 2);
+      const float b0 = (up1 ? acc[2] : acc[0]) + r0, b1 = (up1 ? acc[3] : acc[1]) + r1;
+      float sum = (up2 ? b1 : b0) + __shfl_xor_sync(0xffffffffu, up2 ? b0 : b1, L / 4);
+#pragma unroll
+      for (int o = L / 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (writer) a.out[(size_t)(t0 + tt) * a.out_stride + h * V + my_col] = sum * q_scale;
     }
+    __syncthreads();
   }
-  if (!live) return;
 #pragma unroll
-  for (int n = 0; n < KR4; ++n) {
-    const int i0 = 4 * (ki + 8 * n);
-    if (k4 && i0 + 3 < K) {
-      *reinterpret_cast<float4*>(srow + i0) = make_float4(s[n][0], s[n][1], s[n][2], s[n][3]);
-    } else {
+  for (int c = 0; c < 4; ++c) {
+    if (jc + c >= V) continue;
+    float* srow = sbase + (size_t)(jc + c) * K;
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (i0 + e < K) srow[i0 + e] = s[n][e];
+    for (int n = 0; n < NF; ++n) {
+      const int i0 = 4 * (li + L * n);
+      if (k4 && i0 + 3 < K) {
+        *reinterpret_cast<float4*>(srow + i0) = make_float4(s[n][0][c], s[n][1][c], s[n][2][c], s[n][3][c]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (i0 + e < K) srow[i0 + e] = s[n][e][c];
+      }
     }
   }
 }
 
-template <int KR4>
-int launch_scan(const ScanArgs& a, dim3 grid, cudaStream_t stream) {
+template <int L, int NF>
+int launch_scan(const ScanArgs& a, int blocks_x, cudaStream_t stream) {
+  constexpr int COLS = 4 * (32 / L) * (SCAN_THREADS / 32);
+  const dim3 grid(blocks_x, a.H, (a.V + COLS - 1) / COLS);
   if (a.kind == DECAY_RATE_STEP)
-    return launch_pdl(linear_recurrence_kernel<KR4, false>, grid, SCAN_THREADS, 0, stream, a);
-  return launch_pdl(linear_recurrence_kernel<KR4, true>, grid, SCAN_THREADS, 0, stream, a);
+    return launch_pdl(linear_recurrence_kernel<L, NF, false>, grid, SCAN_THREADS, 0, stream, a);
+  return launch_pdl(linear_recurrence_kernel<L, NF, true>, grid, SCAN_THREADS, 0, stream, a);
+}
+
+// z[r][i] = sigmoid(z[r][i] + b[i])^c in place: the decay of gated linear attention from the
+// output of its low-rank projection, made once per token and key channel (inside the recurrence
+// every block of value channels would make it again).  log sigmoid(x) = -softplus(-x).
+__global__ void bias_sigmoid_pow_kernel(float* __restrict__ z, const float* __restrict__ b, long long total,
+                                        int n, float c) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float x = z[i] + (b ? b[i % n] : 0.f);
+    z[i] = expf(-c * softplus_f(-x));
+  }
 }
 
 // ---- short causal convolution per channel, bias, silu
@@ -196,14 +300,14 @@ int launch_scan(const ScanArgs& a, dim3 grid, cudaStream_t stream) {
 __global__ void causal_conv_silu_kernel(const float* __restrict__ src, int src_stride,
                                         const float* __restrict__ w, const float* __restrict__ b,
                                         const float* __restrict__ hist, long long hist_stride,
-                                        const int* __restrict__ row_slot, const int2* __restrict__ seg,
+                                        const int* __restrict__ row_slot, const int* __restrict__ seg,
                                         int single, float* __restrict__ out, int out_stride, int C, int taps) {
   pdl_trigger();
   pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x, r = blockIdx.x;
   if (c >= C) return;
   const int slot = row_slot[r];
-  const int before = single ? 0 : r - seg[slot].x;       // rows of the request in this step before r
+  const int before = single ? 0 : r - seg[SEG * slot];       // rows of the request in this step before r
   const float* hrow = hist + (size_t)slot * hist_stride + (size_t)c * (taps - 1);
   float acc = b ? b[c] : 0.f;
   for (int j = taps - 1; j >= 0; --j) {       // oldest input first
@@ -217,7 +321,7 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ src, int src_s
 // (request, channel): it reads the old values it still needs before it overwrites them.
 __global__ void conv_history_kernel(const float* __restrict__ src, int src_stride, float* __restrict__ hist,
                                     long long hist_stride, const int* __restrict__ row_slot,
-                                    const int2* __restrict__ seg, int single, int C, int taps) {
+                                    const int* __restrict__ seg, int single, int C, int taps) {
   pdl_trigger();
   pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -227,8 +331,7 @@ __global__ void conv_history_kernel(const float* __restrict__ src, int src_strid
     first = blockIdx.x, end = first + 1, slot = row_slot[first];
   } else {
     slot = blockIdx.x;
-    const int2 s = seg[slot];
-    first = s.x, end = s.y;
+    first = seg[SEG * slot], end = seg[SEG * slot + 1];
   }
   const int n = end - first;
   if (n <= 0) return;
@@ -239,77 +342,109 @@ __global__ void conv_history_kernel(const float* __restrict__ src, int src_strid
   }
 }
 
-// ---- gate and group norm behind the recurrence, one warp per (row, group of `group` channels)
+// ---- gate and group norm behind the recurrence, one block per (row, group of `group` channels)
 //   y = o (+ skip[ch / head] * x)                        the recurrence's output, plus a direct path
 //   gate_first:  out = unit(y * silu(g)) * w             (the gate comes before the norm)
 //   otherwise:   out = unit(y) * w * silu(g)
 // unit(.) divides a group by its root mean square (eps inside the root); w is indexed by the
 // channel modulo w_period (a weight per channel, or one per position in a head shared by heads).
-template <typename TOut>
-__global__ void gated_group_norm_kernel(const float* __restrict__ o, int o_stride, const float* __restrict__ x,
-                                        int x_stride, const float* __restrict__ skip, int head,
-                                        const float* __restrict__ g, int g_stride, const float* __restrict__ w,
-                                        int w_period, TOut* __restrict__ out, int out_stride, int rows,
-                                        int groups, int group, float eps, int gate_first) {
+// A thread keeps up to GN_KEEP of its values between the sum and the scaling; a group larger
+// than GN_KEEP * THREADS reads the rest twice.
+constexpr int GN_KEEP = 8;
+template <typename TOut, int THREADS>
+__global__ void __launch_bounds__(THREADS) gated_group_norm_kernel(
+    const float* __restrict__ o, int o_stride, const float* __restrict__ x, int x_stride,
+    const float* __restrict__ skip, int head, const float* __restrict__ g, int g_stride,
+    const float* __restrict__ w, int w_period, TOut* __restrict__ out, int out_stride, int groups, int group,
+    float eps, int gate_first) {
+  __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
-  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= (long long)rows * groups) return;
-  const int r = (int)(item / groups), gi = (int)(item % groups), lane = threadIdx.x & 31;
+  const int r = blockIdx.x / groups, gi = blockIdx.x - r * groups;
   const int c0 = gi * group;
+  float y[GN_KEEP], gate[GN_KEEP];
   float ss = 0.f;
-  for (int i = lane; i < group; i += 32) {
-    const int ch = c0 + i;
-    float y = o[(size_t)r * o_stride + ch];
-    if (skip) y = fmaf(skip[ch / head], x[(size_t)r * x_stride + ch], y);
-    if (gate_first) y *= silu_f(g[(size_t)r * g_stride + ch]);
-    ss = fmaf(y, y, ss);
+  auto value = [&](int ch, float& gt) {
+    float v = o[(size_t)r * o_stride + ch];
+    if (skip) v = fmaf(skip[ch / head], x[(size_t)r * x_stride + ch], v);
+    gt = silu_f(g[(size_t)r * g_stride + ch]);
+    if (gate_first) v *= gt;
+    return v;
+  };
+#pragma unroll
+  for (int n = 0; n < GN_KEEP; ++n) {
+    const int i = threadIdx.x + n * THREADS;
+    y[n] = 0.f, gate[n] = 0.f;
+    if (i < group) {
+      y[n] = value(c0 + i, gate[n]);
+      ss = fmaf(y[n], y[n], ss);
+    }
   }
-  ss = warp_sum(ss);
+  for (int i = threadIdx.x + GN_KEEP * THREADS; i < group; i += THREADS) {
+    float gt;
+    const float v = value(c0 + i, gt);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / (float)group + eps);
-  for (int i = lane; i < group; i += 32) {
+#pragma unroll
+  for (int n = 0; n < GN_KEEP; ++n) {
+    const int i = threadIdx.x + n * THREADS;
+    if (i < group) {
+      const int ch = c0 + i;
+      float v = y[n] * scale * w[ch % w_period];
+      if (!gate_first) v *= gate[n];
+      out[(size_t)r * out_stride + ch] = from_f32<TOut>(v);
+    }
+  }
+  for (int i = threadIdx.x + GN_KEEP * THREADS; i < group; i += THREADS) {
     const int ch = c0 + i;
-    float y = o[(size_t)r * o_stride + ch];
-    if (skip) y = fmaf(skip[ch / head], x[(size_t)r * x_stride + ch], y);
-    const float gate = silu_f(g[(size_t)r * g_stride + ch]);
-    if (gate_first) y *= gate;
-    y = y * scale * w[ch % w_period];
-    if (!gate_first) y *= gate;
-    out[(size_t)r * out_stride + ch] = from_f32<TOut>(y);
+    float gt;
+    float v = value(ch, gt) * scale * w[ch % w_period];
+    if (!gate_first) v *= gt;
+    out[(size_t)r * out_stride + ch] = from_f32<TOut>(v);
   }
 }
 }  // namespace
 
 LLM_EXPORT int llm_segment_table(const int* row_slot, int rows, int* seg, int n_slots, cudaStream_t stream) {
   if (n_slots <= 0) return 0;
-  return launch_pdl(segment_table_kernel, 1, 256, 0, stream, row_slot, rows, (int2*)seg, n_slots);
+  return launch_pdl(segment_table_kernel, 1, 256, 0, stream, row_slot, rows, seg, n_slots);
 }
 
 // The recurrence over the rows of a step (see the top of this file).  `single`: every row is a
-// request of its own; else `seg` is the table of llm_segment_table over `n_slots` request slots.
-// The state of a (slot, head) is V x K floats, the key channel fastest.
+// request of its own; else `seg` is the table of llm_segment_table and `n_requests` the number of
+// requests that have rows in the step.  The state of a (slot, head) is V x K floats, the key
+// channel fastest.
 LLM_EXPORT int llm_linear_recurrence(const float* q, int q_stride, const float* k, int k_stride, const float* v,
                                      int v_stride, const float* d, int d_stride, const float* p0,
                                      const float* p1, float c, float q_scale, float* state,
                                      long long state_stride, float* out, int out_stride, const int* seg,
-                                     const int* row_slot, int rows, int n_slots, int single, int H, int G, int K,
-                                     int V, int kind, cudaStream_t stream) {
+                                     const int* row_slot, int rows, int n_requests, int single, int H, int G,
+                                     int K, int V, int kind, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || kind < 0 || kind > 2) return LLM_ERR_ARGUMENT;
   if (kind == DECAY_RATE_STEP && (!p0 || !p1)) return LLM_ERR_ARGUMENT;
-  if (!single && !seg) return LLM_ERR_ARGUMENT;
+  if (!single && (!seg || n_requests <= 0)) return LLM_ERR_ARGUMENT;
   if (K > 256) return LLM_ERR_UNSUPPORTED;
   ScanArgs a;
   a.q = q, a.q_stride = q_stride, a.k = k, a.k_stride = k_stride, a.v = v, a.v_stride = v_stride;
   a.d = d, a.d_stride = d_stride, a.p0 = p0, a.p1 = p1, a.c = c, a.q_scale = q_scale;
   a.state = state, a.state_stride = state_stride, a.out = out, a.out_stride = out_stride;
-  a.seg = (const int2*)seg, a.row_slot = row_slot;
+  a.seg = seg, a.row_slot = row_slot;
   a.single = single, a.H = H, a.G = G, a.K = K, a.V = V, a.kind = kind;
-  const dim3 grid(single ? rows : n_slots, H, (V + SCAN_COLS - 1) / SCAN_COLS);
-  if (K <= 32) return launch_scan<1>(a, grid, stream);
-  if (K <= 64) return launch_scan<2>(a, grid, stream);
-  if (K <= 128) return launch_scan<4>(a, grid, stream);
-  return launch_scan<8>(a, grid, stream);
+  const int bx = single ? rows : n_requests;
+  if (K <= 32) return launch_scan<8, 1>(a, bx, stream);
+  if (K <= 64) return launch_scan<16, 1>(a, bx, stream);
+  if (K <= 128) return launch_scan<32, 1>(a, bx, stream);
+  return launch_scan<32, 2>(a, bx, stream);
+}
+
+LLM_EXPORT int llm_bias_sigmoid_pow(float* z, const float* b, int rows, int n, float c, cudaStream_t stream) {
+  const long long total = (long long)rows * n;
+  if (total <= 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
+  return launch_pdl(bias_sigmoid_pow_kernel, blocks, 256, 0, stream, z, b, total, n, c);
 }
 
 // The convolution of `C` channels over the rows of a step, then the request's history of inputs
@@ -321,10 +456,10 @@ LLM_EXPORT int llm_causal_conv_silu(const float* src, int src_stride, const floa
   if (rows <= 0 || C <= 0) return 0;
   if (taps < 1 || (!single && !seg)) return LLM_ERR_ARGUMENT;
   int rc = launch_pdl(causal_conv_silu_kernel, dim3(rows, (C + 127) / 128), 128, 0, stream, src, src_stride, w, b,
-                      (const float*)hist, hist_stride, row_slot, (const int2*)seg, single, out, out_stride, C, taps);
+                      (const float*)hist, hist_stride, row_slot, seg, single, out, out_stride, C, taps);
   if (rc != 0 || taps == 1) return rc;
   return launch_pdl(conv_history_kernel, dim3(single ? rows : n_slots, (C + 127) / 128), 128, 0, stream, src,
-                    src_stride, hist, hist_stride, row_slot, (const int2*)seg, single, C, taps);
+                    src_stride, hist, hist_stride, row_slot, seg, single, C, taps);
 }
 
 LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x, int x_stride,
@@ -334,12 +469,23 @@ LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x
   if (rows <= 0 || groups <= 0) return 0;
   if (group <= 0 || w_period <= 0 || (skip && (!x || head <= 0))) return LLM_ERR_ARGUMENT;
   const long long items = (long long)rows * groups;
-  const int blocks = (int)((items + 3) / 4);
-  if (out_dtype == LLM_F32)
-    return launch_pdl(gated_group_norm_kernel<float>, blocks, 128, 0, stream, o, o_stride, x, x_stride, skip, head,
-                      g, g_stride, w, w_period, (float*)out, out_stride, rows, groups, group, eps, gate_first);
-  if (out_dtype == LLM_BF16)
-    return launch_pdl(gated_group_norm_kernel<bf16>, blocks, 128, 0, stream, o, o_stride, x, x_stride, skip, head,
-                      g, g_stride, w, w_period, (bf16*)out, out_stride, rows, groups, group, eps, gate_first);
+  if (items > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
+  const int blocks = (int)items;
+#define GN(T, TH)                                                                                          \
+  return launch_pdl(gated_group_norm_kernel<T, TH>, blocks, TH, 0, stream, o, o_stride, x, x_stride, skip,  \
+                    head, g, g_stride, w, w_period, (T*)out, out_stride, groups, group, eps, gate_first)
+  if (out_dtype == LLM_F32) {
+    if (group <= 64) GN(float, 32);
+    if (group <= 512) GN(float, 64);
+    if (group <= 2048) GN(float, 256);
+    GN(float, 1024);
+  }
+  if (out_dtype == LLM_BF16) {
+    if (group <= 64) GN(bf16, 32);
+    if (group <= 512) GN(bf16, 64);
+    if (group <= 2048) GN(bf16, 256);
+    GN(bf16, 1024);
+  }
+#undef GN
   return LLM_ERR_UNSUPPORTED;
 }

@@ -74,6 +74,7 @@ def _signatures():
         "llm_norm_scale_add": [P, P, P, P, I, I, F, P],
         "llm_head_gate": [P, I, P, I, I, I, I, I, P],
         "llm_segment_table": [P, I, P, I, P],
+        "llm_bias_sigmoid_pow": [P, P, I, I, F, P],
         "llm_linear_recurrence": [P, I, P, I, P, I, P, I, P, P, F, F, P, L, P, I, P, P, I, I, I, I,
                                   I, I, I, I, P],
         "llm_causal_conv_silu": [P, I, P, P, P, L, P, P, I, I, I, P, I, I, I, P],
@@ -380,10 +381,13 @@ def head_gate(out: torch.Tensor, gate: torch.Tensor, num_heads: int, head_dim: i
 
 
 def segment_table(row_slot: torch.Tensor, seg: torch.Tensor) -> None:
-    """seg[s] = (first row, row after the last) of the step's rows whose request slot is s,
-    (0, 0) for a slot without rows; int32 [slots, 2], made on the device from ``row_slot``."""
+    """seg[s, :2] = (first row, row after the last) of the step's rows whose request slot is s,
+    (0, 0) for a slot without rows; seg[i, 2] = the slot of the i-th request that has rows (in
+    no particular order; -1 behind the last); int32 [slots, 3], made on the device from
+    ``row_slot``."""
     _cuda(row_slot, seg)
     assert row_slot.dtype == torch.int32 and seg.dtype == torch.int32 and seg.is_contiguous()
+    assert seg.dim() == 2 and seg.shape[1] == 3
     _check(lib().llm_segment_table(_ptr(row_slot), row_slot.numel(), _ptr(seg), seg.shape[0],
                                    _stream()), "segment_table")
 
@@ -396,7 +400,7 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torc
                       seg: Optional[torch.Tensor], heads: int, groups: int, key_dim: int,
                       value_dim: int, kind: int, q_scale: float = 1.0, exponent: float = 1.0,
                       rate_log: Optional[torch.Tensor] = None,
-                      step_bias: Optional[torch.Tensor] = None) -> None:
+                      step_bias: Optional[torch.Tensor] = None, n_requests: int = 0) -> None:
     """Per request and head ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_scale q_t)`` over
     the rows of the step in order.  q, k float32 [rows, groups * key_dim], v and out float32
     [rows, heads * value_dim] (column slices of wider matrices are fine); head h uses group
@@ -405,8 +409,9 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torc
     comes from ``d``: DECAY_VECTOR ``a = d`` and DECAY_SIGMOID_POW ``a = sigmoid(d)^exponent``
     with d [rows, heads * key_dim]; DECAY_RATE_STEP with d [rows, heads]:
     ``step = softplus(d + step_bias[h])``, ``a = exp(-exp(rate_log[h]) step)`` and v is
-    multiplied by step.  ``seg``: the table of :func:`segment_table`, or None when every row
-    is a request of its own."""
+    multiplied by step.  ``seg``: the table of :func:`segment_table` with ``n_requests`` the
+    number of requests that have rows in the step, or None when every row is a request of its
+    own."""
     _cuda(q, k, v, d, state, out, row_slot, seg, rate_log, step_bias)
     for t in (q, k, v, d, state, out):
         assert t.dtype == torch.float32 and t.stride(-1) == 1
@@ -416,8 +421,18 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torc
         _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(d), d.stride(0),
         _ptr(rate_log), _ptr(step_bias), float(exponent), float(q_scale), _ptr(state),
         state.stride(0), _ptr(out), out.stride(0), _ptr(seg), _ptr(row_slot), rows,
-        state.shape[0], int(seg is None), heads, groups, key_dim, value_dim, kind, _stream()),
+        int(n_requests), int(seg is None), heads, groups, key_dim, value_dim, kind, _stream()),
         f"linear_recurrence (key_dim {key_dim})")
+
+
+def bias_sigmoid_pow(z: torch.Tensor, bias: Optional[torch.Tensor], exponent: float) -> None:
+    """z = sigmoid(z + bias)^exponent in place (float32 [rows, n], contiguous), in 32-bit through
+    ``exp(-exponent * softplus(-(z + bias)))``."""
+    _cuda(z, bias)
+    assert z.dtype == torch.float32 and z.is_contiguous() and z.dim() == 2
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == z.shape[1])
+    _check(lib().llm_bias_sigmoid_pow(_ptr(z), _ptr(bias), z.shape[0], z.shape[1],
+                                      float(exponent), _stream()), "bias_sigmoid_pow")
 
 
 def causal_conv_silu(src: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],

@@ -37,7 +37,7 @@ def step_segments(ctx: StepContext) -> Optional[torch.Tensor]:
         return None
     seg = ctx.shared.get("segments")
     if seg is None:
-        seg = ctx.buffer("segments", (ctx.cache.max_requests, 2), torch.int32)
+        seg = ctx.buffer("segments", (ctx.cache.max_requests, 3), torch.int32)
         kernels.segment_table(ctx.row_slot, seg)
         ctx.shared["segments"] = seg
     return seg
@@ -80,7 +80,9 @@ class GatedLinearAttention:
         hk, hv = self.heads * self.key_dim, self.heads * self.value_dim
         self.col_k, self.col_v, self.col_g, self.col_a = hk, 2 * hk, 2 * hk + hv, 2 * hk + 2 * hv
         self.in_proj = _padded_rows([t["q"], t["k"], t["v"], t["g"], t["a1"]], self.hidden)
-        self.decay_proj = Linear(t["a2"], optional_tensor_of(spec, "a2_bias", weights))
+        self.decay_proj = Linear(t["a2"])
+        bias = optional_tensor_of(spec, "a2_bias", weights)
+        self.decay_bias = None if bias is None else _f32(bias, device)
         self.o_proj = Linear(t["o"])
         self.norm_weight = _f32(tensor_of(spec, "norm", weights), device)
         if self.norm_weight.numel() != self.value_dim:
@@ -107,11 +109,13 @@ class GatedLinearAttention:
             low = low16
         z = ctx.buffer("gla.z", (rows, H * K), torch.float32)
         self.decay_proj(low, z)
+        # the decay of every (token, key channel), once: bias, sigmoid and the root in one pass
+        kernels.bias_sigmoid_pow(z, self.decay_bias, 1.0 / self.tau)
         o = ctx.buffer("gla.o", (rows, H * V), torch.float32)
         kernels.linear_recurrence(
             proj[:, :self.col_k], proj[:, self.col_k:self.col_v], proj[:, self.col_v:self.col_g],
-            z, state, o, ctx.row_slot, step_segments(ctx), H, H, K, V,
-            kernels.DECAY_SIGMOID_POW, q_scale=K ** -0.5, exponent=1.0 / self.tau)
+            z, state, o, ctx.row_slot, step_segments(ctx), H, H, K, V, kernels.DECAY_VECTOR,
+            q_scale=K ** -0.5, n_requests=len(ctx.segments))
         gated = ctx.buffer("gla.gated", (rows, H * V))
         kernels.gated_group_norm(o, proj[:, self.col_g:self.col_a], self.norm_weight, gated,
                                  group=V, eps=self.eps, gate_first=False)
@@ -178,7 +182,8 @@ class StateSpaceMixer:
         kernels.linear_recurrence(
             xbc[:, self.inner + G * N:], xbc[:, self.inner:self.inner + G * N], xbc[:, :self.inner],
             proj[:, self.col_dt:self.col_dt + H], state, o, ctx.row_slot, seg, H, G, N, P,
-            kernels.DECAY_RATE_STEP, rate_log=self.rate_log, step_bias=self.step_bias)
+            kernels.DECAY_RATE_STEP, rate_log=self.rate_log, step_bias=self.step_bias,
+            n_requests=len(ctx.segments))
         gated = ctx.buffer("ssm.gated", (rows, self.inner))
         kernels.gated_group_norm(o, proj[:, :self.inner], self.norm_weight, gated,
                                  group=self.inner // self.norm_groups, eps=self.eps,

@@ -97,7 +97,7 @@ def _segments(rows_per_slot, n_slots, device):
 
     row_slot = torch.tensor([s for s, n in rows_per_slot for _ in range(n)], dtype=torch.int32,
                             device=device)
-    seg = torch.full((n_slots, 2), -7, dtype=torch.int32, device=device)
+    seg = torch.full((n_slots, 3), -7, dtype=torch.int32, device=device)
     kernels.segment_table(row_slot, seg)
     return row_slot, seg
 
@@ -105,7 +105,9 @@ def _segments(rows_per_slot, n_slots, device):
 @pytest.mark.gpu
 def test_segment_table():
     row_slot, seg = _segments([(3, 5), (0, 1), (2, 7)], 5, "cuda:0")
-    assert seg.cpu().tolist() == [[5, 6], [0, 0], [6, 13], [0, 5], [0, 0]]
+    table = seg.cpu().numpy()
+    assert table[:, :2].tolist() == [[5, 6], [0, 0], [6, 13], [0, 5], [0, 0]]
+    assert sorted(table[:3, 2].tolist()) == [0, 2, 3] and table[3:, 2].tolist() == [-1, -1]
 
 
 @pytest.mark.gpu
@@ -148,7 +150,7 @@ def test_linear_recurrence_kernel(kind, H, G, K, V):
             wide[:, :G * K], wide[:, G * K:2 * G * K], wide[:, 2 * G * K:2 * G * K + H * V], dd,
             state, out, row_slot, None if single else seg, H, G, K, V, kind, q_scale=0.5,
             exponent=0.25, rate_log=torch.from_numpy(p0).to(dev, torch.float32),
-            step_bias=torch.from_numpy(p1).to(dev, torch.float32))
+            step_bias=torch.from_numpy(p1).to(dev, torch.float32), n_requests=len(step))
         ref = np.zeros((rows, H, V))
         r = 0
         for slot, n in step:
@@ -227,6 +229,11 @@ def test_elementwise_kernels_of_the_block(dtype):
     out = torch.zeros(rows, 40, dtype=dtype, device=dev)
     kernels.cast_rows(xt[:, 13:53], out)
     assert torch.equal(out, xt[:, 13:53].to(dtype))
+    # the decay of gated linear attention from its projection
+    z, zb = rng.standard_normal((rows, 24)) * 3, rng.standard_normal(24)
+    zt = torch.from_numpy(z).to(dev, torch.float32)
+    kernels.bias_sigmoid_pow(zt, torch.from_numpy(zb).to(dev, torch.float32), 1 / 16)
+    assert_close(zt.cpu().numpy(), VP.sigmoid(z + zb) ** (1 / 16), "float32", "bias_sigmoid_pow", 1e-6)
     # gate per head
     H, hd = 3, 20
     o = torch.from_numpy(rng.standard_normal((rows, H * hd))).to(dev, dtype)
