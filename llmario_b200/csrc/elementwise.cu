@@ -417,9 +417,11 @@ LLM_EXPORT int llm_cast_rows(const float* x, long long x_stride, void* out, int 
 }
 
 // x[r][:] += y[r][:] * rsqrt(mean(y[r]^2) + eps) * w[:] * s[:]: the norm of a sublayer's output,
-// a scale per channel (s may be null), and the residual sum, all in 32-bit.
+// a scale per channel (s may be null), and the residual sum, all in 32-bit.  With `h` the new x
+// is also written there rounded to bfloat16: the next sublayer's input, without a pass of its own.
 __global__ void norm_scale_add_kernel(const float* __restrict__ y, const float* __restrict__ w,
-                                      const float* __restrict__ s, float* __restrict__ x, int width, float eps) {
+                                      const float* __restrict__ s, float* __restrict__ x,
+                                      bf16* __restrict__ h, int width, float eps) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -435,15 +437,17 @@ __global__ void norm_scale_add_kernel(const float* __restrict__ y, const float* 
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = yr[i] * scale * w[i];
     if (s) v *= s[i];
-    x[r * width + i] += v;
+    v += x[r * width + i];
+    x[r * width + i] = v;
+    if (h) h[r * width + i] = __float2bfloat16_rn(v);
   }
 }
 
-LLM_EXPORT int llm_norm_scale_add(const float* y, const float* w, const float* s, float* x, int rows,
+LLM_EXPORT int llm_norm_scale_add(const float* y, const float* w, const float* s, float* x, void* h, int rows,
                                   int width, float eps, cudaStream_t stream) {
   if (rows <= 0 || width <= 0) return 0;
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  return launch_pdl(norm_scale_add_kernel, rows, threads, 0, stream, y, w, s, x, width, eps);
+  return launch_pdl(norm_scale_add_kernel, rows, threads, 0, stream, y, w, s, x, (bf16*)h, width, eps);
 }
 
 // out[r][h][:] *= sigmoid(gate[r * gate_stride + h]): one gate per (row, head) on the output of

@@ -84,22 +84,35 @@ class OutputNormResidualBlock:
         return graph_safe(self.mixer) and graph_safe(self.feed_forward)
 
     @staticmethod
-    def _input(ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
+    def _input(ctx: StepContext, x: torch.Tensor, have: bool) -> torch.Tensor:
+        """The residual stream as a sublayer reads it: rounded to the activation type.
+        ``have``: the kernel that last added into the stream has left the rounded copy behind
+        (see ``_add``); else (the first sublayer behind the embedding, or behind a block of
+        another kind) it is rounded here."""
         if ctx.dtype == torch.float32:
             return x                   # the sublayer only reads it; x changes after it is done
         h = ctx.buffer("block.h", x.shape)
-        kernels.cast_rows(x, h)
+        if not have:
+            kernels.cast_rows(x, h)
         return h
+
+    @staticmethod
+    def _add(ctx: StepContext, y, norm, scale, x) -> None:
+        """x += scale * norm(y), and the next sublayer's input beside it."""
+        h = ctx.buffer("block.h", x.shape) if ctx.dtype != torch.float32 else None
+        kernels.norm_scale_add(y, norm.weight, scale, x, norm.eps, rounded=h)
 
     def forward(self, ctx: StepContext, call: BoundCall, x: torch.Tensor) -> None:
         y = ctx.buffer("block.y", x.shape, torch.float32)
+        # the run-order entry just before this one was a block of this kind on the same stream
+        have = ctx.shared.get("block.h behind") == (x.data_ptr(), call.index - 1)
         self.mixer.forward(ctx, call.for_need(0) if call.cache_entries else call,
-                           self._input(ctx, x), y, accumulate=False)
-        kernels.norm_scale_add(y, self.mixer_norm.weight, self.mixer_scale, x,
-                               self.mixer_norm.eps)
+                           self._input(ctx, x, have), y, accumulate=False)
+        self._add(ctx, y, self.mixer_norm, self.mixer_scale, x)
         if self.has_feed_forward:
-            self.feed_forward.forward(ctx, self._input(ctx, x), y, accumulate=False)
-            kernels.norm_scale_add(y, self.ffn_norm.weight, self.ffn_scale, x, self.ffn_norm.eps)
+            self.feed_forward.forward(ctx, self._input(ctx, x, True), y, accumulate=False)
+            self._add(ctx, y, self.ffn_norm, self.ffn_scale, x)
+        ctx.shared["block.h behind"] = (x.data_ptr(), call.index)
 
 
 register_part("block", "pre_norm_residual", PreNormResidualBlock, replace=True)

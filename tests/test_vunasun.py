@@ -221,10 +221,12 @@ def test_elementwise_kernels_of_the_block(dtype):
     # norm of the sublayer's output, scale, residual sum
     y, w, s, x = (rng.standard_normal(sh) for sh in ((rows, width), width, width, (rows, width)))
     xt = torch.from_numpy(x).to(dev, torch.float32)
+    h16 = torch.zeros(rows, width, dtype=torch.bfloat16, device=dev)
     kernels.norm_scale_add(torch.from_numpy(y).to(dev, torch.float32),
                            torch.from_numpy(w).to(dev, torch.float32),
-                           torch.from_numpy(s).to(dev, torch.float32), xt, 1e-3)
+                           torch.from_numpy(s).to(dev, torch.float32), xt, 1e-3, rounded=h16)
     assert_close(xt.cpu().numpy(), x + VP.rms_norm(y, w, 1e-3) * s, "float32", "norm_scale_add", 1e-5)
+    assert torch.equal(h16, xt.to(torch.bfloat16))          # the next sublayer's input beside it
     # rounding a column slice
     out = torch.zeros(rows, 40, dtype=dtype, device=dev)
     kernels.cast_rows(xt[:, 13:53], out)
@@ -383,6 +385,20 @@ def test_mixed_batches_and_reused_slots(name, dtype):
         assert sorted(got[r]) == list(range(lengths[r]))
         check_request(got[r], name, toks[r], dtype, f"request {r}", seed=0)
     assert runner.cache.free_slots() == 4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ("attn_g8", "attn_g3", "attn_tc", "mix"))
+def test_a_long_prompt_over_many_chunks_and_the_engine_page(name, dtype):
+    """A prompt of several tensor-core tiles with the engine's default page of 64, then a second
+    portion that starts inside a chunk and a page, then single tokens."""
+    toks = tokens_for(name, 420, 6)
+    runner = runner_for(name, dtype, page_size=64, cache_tokens=1024)
+    steps = [[("a", toks[:333], range(333))], [("a", toks[333:410], range(77))]] \
+        + [[("a", [t], [0])] for t in toks[410:]]
+    got = run_steps(runner, steps)
+    check_request(got["a"], name, toks, dtype, "long prompt")
 
 
 @pytest.mark.gpu

@@ -61,6 +61,11 @@ CONFIGS: Dict[str, dict] = {
                                     scale=0.2)]),
     "attn_odd": config([attention(heads=3, kv_heads=1, dim=20, chunk=7, rot=10)], width=60,
                        vocab=77),
+    # three query heads to a key head (no tensor-core tile takes it), and eight with whole heads
+    # of 128 rotated and a chunk that is no multiple of a page
+    "attn_g3": config([attention(heads=6, kv_heads=2, dim=64, chunk=36, rot=16)], width=96),
+    "attn_g8": config([attention(heads=8, kv_heads=1, dim=128, chunk=100, rot=128,
+                                 mlp=dense(64))], width=64),
     # all of them, in an order of their own
     "mix": config([attention(chunk=48, mlp=dense(96)), mamba2(norm_groups=2), gla(),
                    attention(heads=2, kv_heads=1, dim=64, chunk=16, rot=32, base=500.0),
