@@ -419,14 +419,15 @@ LLM_EXPORT int llm_cast_rows(const float* x, long long x_stride, void* out, int 
 // x[r][:] += y[r][:] * rsqrt(mean(y[r]^2) + eps) * w[:] * s[:]: the norm of a sublayer's output,
 // a scale per channel (s may be null), and the residual sum, all in 32-bit.  With `h` the new x
 // is also written there rounded to bfloat16: the next sublayer's input, without a pass of its own.
-__global__ void norm_scale_add_kernel(const float* __restrict__ y, const float* __restrict__ w,
+// With `clear` y is left holding zeros (the product that fills it adds partial sums into it).
+__global__ void norm_scale_add_kernel(float* __restrict__ y, const float* __restrict__ w,
                                       const float* __restrict__ s, float* __restrict__ x,
-                                      bf16* __restrict__ h, int width, float eps) {
+                                      bf16* __restrict__ h, int width, float eps, int clear) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
   const size_t r = blockIdx.x;
-  const float* yr = y + r * width;
+  float* yr = y + r * width;
   float ss = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float v = yr[i];
@@ -436,6 +437,7 @@ __global__ void norm_scale_add_kernel(const float* __restrict__ y, const float* 
   const float scale = 1.0f / sqrtf(ss / (float)width + eps);
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = yr[i] * scale * w[i];
+    if (clear) yr[i] = 0.f;
     if (s) v *= s[i];
     v += x[r * width + i];
     x[r * width + i] = v;
@@ -443,11 +445,66 @@ __global__ void norm_scale_add_kernel(const float* __restrict__ y, const float* 
   }
 }
 
-LLM_EXPORT int llm_norm_scale_add(const float* y, const float* w, const float* s, float* x, void* h, int rows,
-                                  int width, float eps, cudaStream_t stream) {
+// The same for widths that are multiples of four and at most 256 * 4 * VEC_MAX: the row of y is
+// read once with 16-byte loads and kept in registers between the sum and the scaling.
+__global__ void __launch_bounds__(256) norm_scale_add_vec_kernel(float* __restrict__ y, const float* __restrict__ w,
+                                                                 const float* __restrict__ s, float* __restrict__ x,
+                                                                 bf16* __restrict__ h, int width, float eps,
+                                                                 int clear) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const size_t r = blockIdx.x;
+  float4* yr = reinterpret_cast<float4*>(y + r * width);
+  float4* xr = reinterpret_cast<float4*>(x + r * width);
+  const float4* wr = reinterpret_cast<const float4*>(w);
+  const float4* sr = reinterpret_cast<const float4*>(s);
+  const int n4 = width >> 2;
+  float4 v[VEC_MAX];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VEC_MAX; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < n4) {
+      v[k] = yr[i];
+      if (clear) yr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+  for (int k = 0; k < VEC_MAX; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < n4) {
+      const float4 g = wr[i], o = xr[i];
+      float a = v[k].x * scale * g.x, b = v[k].y * scale * g.y, c = v[k].z * scale * g.z,
+            d = v[k].w * scale * g.w;
+      if (s) {
+        const float4 t = sr[i];
+        a *= t.x, b *= t.y, c *= t.z, d *= t.w;
+      }
+      a += o.x, b += o.y, c += o.z, d += o.w;
+      xr[i] = make_float4(a, b, c, d);
+      if (h) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(h + r * width + 4 * i) = packed;
+      }
+    }
+  }
+}
+
+LLM_EXPORT int llm_norm_scale_add(float* y, const float* w, const float* s, float* x, void* h, int rows,
+                                  int width, float eps, int clear, cudaStream_t stream) {
   if (rows <= 0 || width <= 0) return 0;
+  if (width % 4 == 0 && width <= 256 * 4 * VEC_MAX &&
+      (((uintptr_t)y | (uintptr_t)w | (uintptr_t)s | (uintptr_t)x | (uintptr_t)h) & 15) == 0)
+    return launch_pdl(norm_scale_add_vec_kernel, rows, 256, 0, stream, y, w, s, x, (bf16*)h, width, eps, clear);
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  return launch_pdl(norm_scale_add_kernel, rows, threads, 0, stream, y, w, s, x, (bf16*)h, width, eps);
+  return launch_pdl(norm_scale_add_kernel, rows, threads, 0, stream, y, w, s, x, (bf16*)h, width, eps, clear);
 }
 
 // out[r][h][:] *= sigmoid(gate[r * gate_stride + h]): one gate per (row, head) on the output of

@@ -71,7 +71,7 @@ def _signatures():
         "llm_random_normal": [P, I, L, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, L,
                               P],
         "llm_cast_rows": [P, L, P, I, L, I, I, P],
-        "llm_norm_scale_add": [P, P, P, P, P, I, I, F, P],
+        "llm_norm_scale_add": [P, P, P, P, P, I, I, F, I, P],
         "llm_head_gate": [P, I, P, I, I, I, I, I, P],
         "llm_segment_table": [P, I, P, I, P],
         "llm_bias_sigmoid_pow": [P, P, I, I, F, P],
@@ -358,9 +358,11 @@ def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def norm_scale_add(y: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor],
-                   x: torch.Tensor, eps: float, rounded: Optional[torch.Tensor] = None) -> None:
+                   x: torch.Tensor, eps: float, rounded: Optional[torch.Tensor] = None,
+                   clear: bool = False) -> None:
     """x += y * rsqrt(mean(y^2) + eps) * weight (* scale): all float32, row by row.  ``rounded``
-    (bfloat16, x's shape) also receives the new x, rounded once."""
+    (bfloat16, x's shape) also receives the new x, rounded once.  ``clear``: y holds zeros
+    afterwards (a split-K product adds its partial sums into it the next time)."""
     _cuda(y, weight, scale, x, rounded)
     assert rounded is None or (rounded.dtype == torch.bfloat16 and rounded.shape == x.shape
                                and rounded.is_contiguous())
@@ -369,7 +371,7 @@ def norm_scale_add(y: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.
     assert scale is None or (scale.dtype == torch.float32 and scale.numel() == x.shape[1])
     _check(lib().llm_norm_scale_add(_ptr(y), _ptr(weight), _ptr(scale), _ptr(x), _ptr(rounded),
                                     x.shape[0],
-                                    x.shape[1], float(eps), _stream()), "norm_scale_add")
+                                    x.shape[1], float(eps), int(clear), _stream()), "norm_scale_add")
 
 
 def head_gate(out: torch.Tensor, gate: torch.Tensor, num_heads: int, head_dim: int,

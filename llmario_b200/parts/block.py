@@ -97,21 +97,26 @@ class OutputNormResidualBlock:
         return h
 
     @staticmethod
-    def _add(ctx: StepContext, y, norm, scale, x) -> None:
+    def _add(ctx: StepContext, y, norm, scale, x, clear: bool) -> None:
         """x += scale * norm(y), and the next sublayer's input beside it."""
         h = ctx.buffer("block.h", x.shape) if ctx.dtype != torch.float32 else None
-        kernels.norm_scale_add(y, norm.weight, scale, x, norm.eps, rounded=h)
+        kernels.norm_scale_add(y, norm.weight, scale, x, norm.eps, rounded=h, clear=clear)
 
     def forward(self, ctx: StepContext, call: BoundCall, x: torch.Tensor) -> None:
-        y = ctx.buffer("block.y", x.shape, torch.float32)
+        # With few rows the sublayers' last products are cut along K and add partial sums.  Their
+        # destination is then a buffer that is created as zeros and that the residual kernel
+        # clears again once it has read it: the sublayers add into it and no clearing pass runs.
+        kept_zero = ctx.rows <= kernels.SPLIT_K_MAX_ROWS
+        y = ctx.buffer("block.y.z" if kept_zero else "block.y", x.shape, torch.float32,
+                       zero=kept_zero)
         # the run-order entry just before this one was a block of this kind on the same stream
         have = ctx.shared.get("block.h behind") == (x.data_ptr(), call.index - 1)
         self.mixer.forward(ctx, call.for_need(0) if call.cache_entries else call,
-                           self._input(ctx, x, have), y, accumulate=False)
-        self._add(ctx, y, self.mixer_norm, self.mixer_scale, x)
+                           self._input(ctx, x, have), y, accumulate=kept_zero)
+        self._add(ctx, y, self.mixer_norm, self.mixer_scale, x, kept_zero)
         if self.has_feed_forward:
-            self.feed_forward.forward(ctx, self._input(ctx, x, True), y, accumulate=False)
-            self._add(ctx, y, self.ffn_norm, self.ffn_scale, x)
+            self.feed_forward.forward(ctx, self._input(ctx, x, True), y, accumulate=kept_zero)
+            self._add(ctx, y, self.ffn_norm, self.ffn_scale, x, kept_zero)
         ctx.shared["block.h behind"] = (x.data_ptr(), call.index)
 
 
