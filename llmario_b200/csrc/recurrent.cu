@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
   constexpr int KP = 4 * L * NF;                            // key channels, padded
   constexpr int GROUPS = 32 / L;                            // column groups of a warp
   constexpr int COLS = 4 * GROUPS * (SCAN_THREADS / 32);    // value channels of a block
-  constexpr int TC = KP >= 256 ? 4 : (KP >= 128 ? 8 : 16);  // tokens of a chunk
+  constexpr int TC = KP >= 512 ? 2 : (KP >= 256 ? 4 : (KP >= 128 ? 8 : 16));  // tokens of a chunk
   __shared__ __align__(16) float q_s[2][TC][KP];
   __shared__ __align__(16) float k_s[2][TC][KP];
   __shared__ __align__(16) float a_s[2][VEC ? TC : 1][VEC ? KP : 4];
@@ -317,6 +317,46 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ src, int src_s
   out[(size_t)r * out_stride + c] = silu_f(acc);
 }
 
+// The same for 2 to 4 taps with a thread walking a strip of rows of its channel: the weights and
+// the last inputs stay in registers, so a row costs one load and one store.  The order of the
+// sum is that of the kernel above (oldest input first), so both give the same bits.
+template <int TAPS>
+__global__ void causal_conv_silu_strip_kernel(const float* __restrict__ src, int src_stride,
+                                              const float* __restrict__ w, const float* __restrict__ b,
+                                              const float* __restrict__ hist, long long hist_stride,
+                                              const int* __restrict__ row_slot, const int* __restrict__ seg,
+                                              int single, float* __restrict__ out, int out_stride, int rows,
+                                              int C) {
+  constexpr int R = 16;
+  pdl_trigger();
+  pdl_wait();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int r0 = blockIdx.x * R, r1 = min(rows, r0 + R);
+  float wt[TAPS], win[TAPS];     // win[j - 1]: the input j rows back, when that row is in the strip
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) wt[j] = w[(size_t)c * TAPS + j], win[j] = 0.f;
+  const float bias = b ? b[c] : 0.f;
+  for (int r = r0; r < r1; ++r) {
+    const int slot = row_slot[r];
+    const int before = single ? 0 : r - seg[SEG * slot];
+    const float x0 = src[(size_t)r * src_stride + c];
+    float acc = bias;
+#pragma unroll
+    for (int j = TAPS - 1; j >= 1; --j) {
+      float x;
+      if (j <= before) x = r - j >= r0 ? win[j - 1] : src[(size_t)(r - j) * src_stride + c];
+      else x = hist[(size_t)slot * hist_stride + (size_t)c * (TAPS - 1) + TAPS - 1 - (j - before)];
+      acc = fmaf(wt[TAPS - 1 - j], x, acc);
+    }
+    acc = fmaf(wt[TAPS - 1], x0, acc);
+    out[(size_t)r * out_stride + c] = silu_f(acc);
+#pragma unroll
+    for (int j = TAPS - 1; j >= 1; --j) win[j] = win[j - 1];
+    win[0] = x0;
+  }
+}
+
 // hist[slot][c][:] = the last taps - 1 inputs of the request after this step.  A thread owns one
 // (request, channel): it reads the old values it still needs before it overwrites them.
 __global__ void conv_history_kernel(const float* __restrict__ src, int src_stride, float* __restrict__ hist,
@@ -405,6 +445,75 @@ __global__ void __launch_bounds__(THREADS) gated_group_norm_kernel(
     out[(size_t)r * out_stride + ch] = from_f32<TOut>(v);
   }
 }
+// The same with 16-byte reads: the group, every row stride, the head size and the weight's
+// period are multiples of four, so four neighbouring channels share a head and lie together.
+template <typename TOut, int THREADS>
+__global__ void __launch_bounds__(THREADS) gated_group_norm_vec_kernel(
+    const float* __restrict__ o, int o_stride, const float* __restrict__ x, int x_stride,
+    const float* __restrict__ skip, int head, const float* __restrict__ g, int g_stride,
+    const float* __restrict__ w, int w_period, TOut* __restrict__ out, int out_stride, int groups, int group,
+    float eps, int gate_first) {
+  constexpr int KEEP = 2;
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x / groups, gi = blockIdx.x - r * groups;
+  const int c0 = gi * group, n4 = group >> 2;
+  auto value = [&](int ch, float4& gt) {
+    float4 v = *reinterpret_cast<const float4*>(o + (size_t)r * o_stride + ch);
+    if (skip) {
+      const float d = skip[ch / head];
+      const float4 xv = *reinterpret_cast<const float4*>(x + (size_t)r * x_stride + ch);
+      v.x = fmaf(d, xv.x, v.x), v.y = fmaf(d, xv.y, v.y), v.z = fmaf(d, xv.z, v.z), v.w = fmaf(d, xv.w, v.w);
+    }
+    const float4 gv = *reinterpret_cast<const float4*>(g + (size_t)r * g_stride + ch);
+    gt = make_float4(silu_f(gv.x), silu_f(gv.y), silu_f(gv.z), silu_f(gv.w));
+    if (gate_first) v.x *= gt.x, v.y *= gt.y, v.z *= gt.z, v.w *= gt.w;
+    return v;
+  };
+  auto store = [&](int ch, float4 v, const float4& gt, float scale) {
+    const float4 wv = *reinterpret_cast<const float4*>(w + ch % w_period);
+    v.x = v.x * scale * wv.x, v.y = v.y * scale * wv.y, v.z = v.z * scale * wv.z, v.w = v.w * scale * wv.w;
+    if (!gate_first) v.x *= gt.x, v.y *= gt.y, v.z *= gt.z, v.w *= gt.w;
+    TOut* dst = out + (size_t)r * out_stride + ch;
+    if (sizeof(TOut) == 4) {
+      *reinterpret_cast<float4*>(dst) = v;
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(dst) = packed;
+    }
+  };
+  float4 y[KEEP], gate[KEEP];
+  float ss = 0.f;
+#pragma unroll
+  for (int n = 0; n < KEEP; ++n) {
+    const int i = threadIdx.x + n * THREADS;
+    if (i < n4) {
+      y[n] = value(c0 + 4 * i, gate[n]);
+      ss += y[n].x * y[n].x + y[n].y * y[n].y + y[n].z * y[n].z + y[n].w * y[n].w;
+    }
+  }
+  for (int i = threadIdx.x + KEEP * THREADS; i < n4; i += THREADS) {
+    float4 gt;
+    const float4 v = value(c0 + 4 * i, gt);
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)group + eps);
+#pragma unroll
+  for (int n = 0; n < KEEP; ++n) {
+    const int i = threadIdx.x + n * THREADS;
+    if (i < n4) store(c0 + 4 * i, y[n], gate[n], scale);
+  }
+  for (int i = threadIdx.x + KEEP * THREADS; i < n4; i += THREADS) {
+    float4 gt;
+    const float4 v = value(c0 + 4 * i, gt);
+    store(c0 + 4 * i, v, gt, scale);
+  }
+}
 }  // namespace
 
 LLM_EXPORT int llm_segment_table(const int* row_slot, int rows, int* seg, int n_slots, cudaStream_t stream) {
@@ -426,7 +535,7 @@ LLM_EXPORT int llm_linear_recurrence(const float* q, int q_stride, const float* 
   if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || kind < 0 || kind > 2) return LLM_ERR_ARGUMENT;
   if (kind == DECAY_RATE_STEP && (!p0 || !p1)) return LLM_ERR_ARGUMENT;
   if (!single && (!seg || n_requests <= 0)) return LLM_ERR_ARGUMENT;
-  if (K > 256) return LLM_ERR_UNSUPPORTED;
+  if (K > 512) return LLM_ERR_UNSUPPORTED;     // (sixty-four state registers per lane are the most)
   ScanArgs a;
   a.q = q, a.q_stride = q_stride, a.k = k, a.k_stride = k_stride, a.v = v, a.v_stride = v_stride;
   a.d = d, a.d_stride = d_stride, a.p0 = p0, a.p1 = p1, a.c = c, a.q_scale = q_scale;
@@ -437,7 +546,8 @@ LLM_EXPORT int llm_linear_recurrence(const float* q, int q_stride, const float* 
   if (K <= 32) return launch_scan<8, 1>(a, bx, stream);
   if (K <= 64) return launch_scan<16, 1>(a, bx, stream);
   if (K <= 128) return launch_scan<32, 1>(a, bx, stream);
-  return launch_scan<32, 2>(a, bx, stream);
+  if (K <= 256) return launch_scan<32, 2>(a, bx, stream);
+  return launch_scan<32, 4>(a, bx, stream);
 }
 
 LLM_EXPORT int llm_bias_sigmoid_pow(float* z, const float* b, int rows, int n, float c, cudaStream_t stream) {
@@ -455,8 +565,19 @@ LLM_EXPORT int llm_causal_conv_silu(const float* src, int src_stride, const floa
                                     int taps, cudaStream_t stream) {
   if (rows <= 0 || C <= 0) return 0;
   if (taps < 1 || (!single && !seg)) return LLM_ERR_ARGUMENT;
-  int rc = launch_pdl(causal_conv_silu_kernel, dim3(rows, (C + 127) / 128), 128, 0, stream, src, src_stride, w, b,
-                      (const float*)hist, hist_stride, row_slot, seg, single, out, out_stride, C, taps);
+  int rc;
+  const dim3 strips((rows + 15) / 16, (C + 127) / 128);
+#define STRIP(T)                                                                                             \
+  rc = launch_pdl(causal_conv_silu_strip_kernel<T>, strips, 128, 0, stream, src, src_stride, w, b,            \
+                  (const float*)hist, hist_stride, row_slot, seg, single, out, out_stride, rows, C)
+  // (strips pay from a few hundred rows on; a decode step has too few rows to fill the GPU with them)
+  if (taps == 2 && rows >= 256) STRIP(2);
+  else if (taps == 3 && rows >= 256) STRIP(3);
+  else if (taps == 4 && rows >= 256) STRIP(4);
+  else
+    rc = launch_pdl(causal_conv_silu_kernel, dim3(rows, (C + 127) / 128), 128, 0, stream, src, src_stride, w, b,
+                    (const float*)hist, hist_stride, row_slot, seg, single, out, out_stride, C, taps);
+#undef STRIP
   if (rc != 0 || taps == 1) return rc;
   return launch_pdl(conv_history_kernel, dim3(single ? rows : n_slots, (C + 127) / 128), 128, 0, stream, src,
                     src_stride, hist, hist_stride, row_slot, seg, single, C, taps);
@@ -471,6 +592,25 @@ LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x
   const long long items = (long long)rows * groups;
   if (items > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
   const int blocks = (int)items;
+  const bool vec = !((group | o_stride | g_stride | out_stride | w_period) & 3) &&
+                   (!skip || !((head | x_stride) & 3)) &&
+                   !(((uintptr_t)o | (uintptr_t)g | (uintptr_t)w | (uintptr_t)out | (uintptr_t)x) & 15);
+#define GNV(T, TH)                                                                                             \
+  return launch_pdl(gated_group_norm_vec_kernel<T, TH>, blocks, TH, 0, stream, o, o_stride, x, x_stride, skip,  \
+                    head, g, g_stride, w, w_period, (T*)out, out_stride, groups, group, eps, gate_first)
+  if (vec && out_dtype == LLM_F32) {
+    if (group <= 256) GNV(float, 32);
+    if (group <= 512) GNV(float, 64);
+    if (group <= 2048) GNV(float, 256);
+    GNV(float, 1024);
+  }
+  if (vec && out_dtype == LLM_BF16) {
+    if (group <= 256) GNV(bf16, 32);
+    if (group <= 512) GNV(bf16, 64);
+    if (group <= 2048) GNV(bf16, 256);
+    GNV(bf16, 1024);
+  }
+#undef GNV
 #define GN(T, TH)                                                                                          \
   return launch_pdl(gated_group_norm_kernel<T, TH>, blocks, TH, 0, stream, o, o_stride, x, x_stride, skip,  \
                     head, g, g_stride, w, w_period, (T*)out, out_stride, groups, group, eps, gate_first)

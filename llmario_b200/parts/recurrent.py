@@ -69,8 +69,8 @@ class GatedLinearAttention:
         self.eps = float(spec["eps"])
         if self.tau <= 0:
             raise ConfigError(f"gla: tau {self.tau} must be positive")
-        if self.key_dim > 256:
-            raise ConfigError(f"gla: key_dim {self.key_dim}: the recurrence keeps at most 256 key "
+        if self.key_dim > 512:
+            raise ConfigError(f"gla: key_dim {self.key_dim}: the recurrence keeps at most 512 key "
                               "channels of a state column in registers")
         t = {r: tensor_of(spec, r, weights) for r in ("q", "k", "v", "g", "a1", "a2", "o")}
         self.rank = t["a1"].shape[0]          # the decay's low rank: the tensors' own size
@@ -139,8 +139,8 @@ class StateSpaceMixer:
             raise ConfigError(f"mamba2: {self.heads} heads cannot share {self.groups} groups")
         if self.inner % self.norm_groups:
             raise ConfigError(f"mamba2: {self.inner} channels in {self.norm_groups} norm groups")
-        if self.state_dim > 256:
-            raise ConfigError(f"mamba2: state {self.state_dim}: the recurrence keeps at most 256 "
+        if self.state_dim > 512:
+            raise ConfigError(f"mamba2: state {self.state_dim}: the recurrence keeps at most 512 "
                               "state rows of a column in registers")
         if self.taps < 1:
             raise ConfigError("mamba2: the convolution has at least one tap")

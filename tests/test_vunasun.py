@@ -113,7 +113,7 @@ def test_segment_table():
 @pytest.mark.gpu
 @pytest.mark.parametrize("kind", (0, 1, 2))
 @pytest.mark.parametrize("H,G,K,V", [(2, 2, 8, 4), (3, 3, 24, 16), (4, 2, 40, 24), (2, 1, 72, 20),
-                                     (1, 1, 136, 33), (2, 2, 256, 16), (2, 2, 30, 7)])
+                                     (1, 1, 136, 33), (2, 2, 256, 16), (2, 2, 30, 7), (2, 1, 320, 12)])
 def test_linear_recurrence_kernel(kind, H, G, K, V):
     """One kernel, three ways to make the decay, state rows of every register count, value
     channels that do not fill a block, several requests in a step and steps that carry on."""
@@ -178,7 +178,7 @@ def test_linear_recurrence_kernel(kind, H, G, K, V):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("taps", (1, 2, 4))
+@pytest.mark.parametrize("taps", (1, 2, 3, 4, 5))
 def test_causal_convolution_with_history(taps):
     from llmario_b200 import kernels
 
@@ -187,7 +187,8 @@ def test_causal_convolution_with_history(taps):
     w, b = rng.standard_normal((C, taps)), rng.standard_normal(C)
     hist = torch.zeros(n_slots, 11 + C * (taps - 1), dtype=torch.float32, device=dev)
     seen = {s: np.zeros((taps - 1, C)) for s in range(n_slots)}    # inputs so far, zeros before
-    for step in ([(1, 9), (0, 2)], [(0, 1), (1, 1)], [(1, 1), (0, 6)], [(0, 1)]):
+    for step in ([(1, 9), (0, 2)], [(0, 1), (1, 1)], [(1, 1), (0, 6)], [(0, 1)], [(1, 2), (0, 37)],
+                 [(0, 3), (1, 290)], [(1, 1), (0, 1)]):        # (many rows: a thread walks a strip)
         rows = sum(n for _, n in step)
         x = rng.standard_normal((rows, C))
         row_slot, seg = _segments(step, n_slots, dev)
@@ -246,26 +247,28 @@ def test_elementwise_kernels_of_the_block(dtype):
                  1e-5 if dtype == torch.float32 else 8e-3)
     assert float(gate[:, 2:2 + H].abs().max()) == 0.0 and float(gate[:, :2].abs().min()) > 0.0
     # gate and group norm behind the recurrence, both orders, with and without the direct path
-    groups, group, head = 4, 30, 24
-    ch = groups * group
-    oo, xx, gg = (rng.standard_normal((rows, ch)) for _ in range(3))
-    skip = rng.standard_normal(ch // head)
-    for gate_first, wt, use_skip in ((True, rng.standard_normal(ch), True),
-                                     (False, rng.standard_normal(group), False)):
-        yy = oo + (np.repeat(skip, head) * xx if use_skip else 0)
-        gate_v = gg / (1 + np.exp(-gg))
-        if gate_first:
-            ref = VP.rms_unit((yy * gate_v).reshape(rows, groups, group), 1e-4).reshape(rows, ch) * wt
-        else:
-            ref = VP.rms_unit(yy.reshape(rows, groups, group), 1e-4).reshape(rows, ch) \
-                * np.tile(wt, groups) * gate_v
-        res = torch.empty(rows, ch, dtype=dtype, device=dev)
-        f = lambda a: torch.from_numpy(a).to(dev, torch.float32)
-        kernels.gated_group_norm(f(oo), f(gg), f(wt), res, group, 1e-4, gate_first,
-                                 skip=f(skip) if use_skip else None,
-                                 skip_input=f(xx) if use_skip else None, head=head)
-        assert_close(res.float().cpu().numpy(), ref, "float32", "gated_group_norm",
-                     1e-5 if dtype == torch.float32 else 8e-3)
+    # (channels in fours and not: the kernel reads 16-byte pieces where it can; a group larger
+    # than what a thread keeps in registers)
+    for groups, group, head in ((4, 30, 24), (3, 64, 16), (1, 9 * 1024, 48)):
+      ch = groups * group
+      oo, xx, gg = (rng.standard_normal((rows, ch)) for _ in range(3))
+      skip = rng.standard_normal(ch // head)
+      for gate_first, wt, use_skip in ((True, rng.standard_normal(ch), True),
+                                       (False, rng.standard_normal(group), False)):
+          yy = oo + (np.repeat(skip, head) * xx if use_skip else 0)
+          gate_v = gg / (1 + np.exp(-gg))
+          if gate_first:
+              ref = VP.rms_unit((yy * gate_v).reshape(rows, groups, group), 1e-4).reshape(rows, ch) * wt
+          else:
+              ref = VP.rms_unit(yy.reshape(rows, groups, group), 1e-4).reshape(rows, ch) \
+                  * np.tile(wt, groups) * gate_v
+          res = torch.empty(rows, ch, dtype=dtype, device=dev)
+          f = lambda a: torch.from_numpy(a).to(dev, torch.float32)
+          kernels.gated_group_norm(f(oo), f(gg), f(wt), res, group, 1e-4, gate_first,
+                                   skip=f(skip) if use_skip else None,
+                                   skip_input=f(xx) if use_skip else None, head=head)
+          assert_close(res.float().cpu().numpy(), ref, "float32", "gated_group_norm",
+                       1e-5 if dtype == torch.float32 else 8e-3)
 
 
 # --------------------------------------------------------------------------------------------
@@ -471,3 +474,53 @@ def test_greedy_generation_through_the_engine(dtype):
         assert clear > 60
         assert eng.stats()["graph_replays"] > 0
         eng.runner.cache.check_invariants()
+
+
+@pytest.mark.gpu
+def test_command_line_and_trace_runner(tmp_path):
+    """The two programs a user starts: ``llmario-b200 run`` on a Vunasun model folder (greedy ids
+    against the plain implementation) and ``bin/trace_run`` (given tokens in steps, logits in
+    files), which choose the model class by ``config.json``."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "mix"
+    prompt = tokens_for(name, 19, 40)
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "llmario-b200"), "run",
+                        model_dir(name), "--tokens", ",".join(map(str, prompt)), "--max-tokens", "6",
+                        "--dtype", "float32", "--page-size", "16", "--context", "128"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = [int(t) for t in p.stdout.strip().splitlines()[-1].split(",")]
+    assert len(out) == 6
+    ref = plain_logits(name, prompt + out)
+    for j, tok in enumerate(out):
+        l = ref[len(prompt) - 1 + j]
+        top = np.sort(l)[-2:]
+        if top[1] - top[0] > 1e-3 * np.abs(l).max():
+            assert tok == int(np.argmax(l))
+    # the trace runner: two requests, portions beside single tokens, a slot given back and taken
+    a, b, c = (tokens_for(name, n, 50 + i) for i, n in enumerate((40, 7, 12)))
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:25], "want": [0, 24]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[25:26], "want": [0]},
+                                {"id": "b", "tokens": b, "want": [6]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[26:], "want": [13]},
+                                {"id": "c", "tokens": c[:2], "want": []}], "end": ["a"]},
+        {"step": 3, "entries": [{"id": "c", "tokens": c[2:], "want": [0, 9]}], "end": ["c"]},
+    ]
+    out_dir = tmp_path / "out"
+    p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", model_dir(name), "--dtype",
+                        "float32", "--out", str(out_dir), "--max-tokens", "192"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True,
+                       text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    ra, rb, rc = plain_logits(name, a), plain_logits(name, b), plain_logits(name, c)
+    want = {0: np.stack([ra[0], ra[24]]), 1: np.stack([ra[25], rb[6]]), 2: ra[39:40],
+            3: np.stack([rc[2], rc[11]])}
+    for i, ref in want.items():
+        got = np.fromfile(out_dir / f"{i}.f32", dtype="<f4").reshape(ref.shape)
+        assert_close(got, ref, "float32", f"trace step {i}")
