@@ -66,6 +66,12 @@ CONFIGS: Dict[str, dict] = {
     "attn_g3": config([attention(heads=6, kv_heads=2, dim=64, chunk=36, rot=16)], width=96),
     "attn_g8": config([attention(heads=8, kv_heads=1, dim=128, chunk=100, rot=128,
                                  mlp=dense(64))], width=64),
+    # sixteen query heads to a key head
+    "attn_g16": config([attention(heads=16, kv_heads=1, dim=64, chunk=30, rot=32)], width=64),
+    # sizes that are multiples of nothing: every kernel's plain path
+    "odd": config([gla(heads=3, dim=6, vdim=10, tau=2.0, rank=5),
+                   mamba2(heads=3, vdim=5, state=6, groups=3, conv=3, norm_groups=3, mlp=dense(34)),
+                   attention(heads=2, kv_heads=2, dim=10, chunk=5, rot=4)], width=50, vocab=33),
     # all of them, in an order of their own
     "mix": config([attention(chunk=48, mlp=dense(96)), mamba2(norm_groups=2), gla(),
                    attention(heads=2, kv_heads=1, dim=64, chunk=16, rot=32, base=500.0),
