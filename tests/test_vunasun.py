@@ -10,8 +10,8 @@ import pytest
 import torch
 
 from plain import vunasun_plain as VP
-from vunasun_util import (CONFIGS, assert_close, model_dir, needle_model, plain_logits, runner_for,
-                          sensitivity, tokens_for, weights)
+from vunasun_util import (CONFIGS, assert_close, model_dir, needle_model, plain_logits, random_config,
+                          runner_for, sensitivity, tokens_for, weights)
 
 DTYPES = ("float32", "bfloat16")
 
@@ -402,6 +402,21 @@ def test_a_long_prompt_over_many_chunks_and_the_engine_page(name, dtype):
         + [[("a", [t], [0])] for t in toks[410:]]
     got = run_steps(runner, steps)
     check_request(got["a"], name, toks, dtype, "long prompt")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_from_a_seed(seed, dtype):
+    """Layers of any kind in any order with sizes drawn from a seed, the engine's page of 64:
+    a prompt in portions, then single tokens, against the plain implementation."""
+    name = random_config(seed)
+    toks = tokens_for(name, 230, 7)
+    runner = runner_for(name, dtype, page_size=64, cache_tokens=512)
+    steps = [[("a", toks[:150], range(150))], [("a", toks[150:153], range(3))],
+             [("a", toks[153:200], range(47))]] + [[("a", [t], [0])] for t in toks[200:]]
+    got = run_steps(runner, steps)
+    check_request(got["a"], name, toks, dtype, f"{name} {CONFIGS[name]['layers']}")
 
 
 @pytest.mark.gpu
