@@ -90,10 +90,10 @@ def random_config(seed: int) -> str:
     pick = lambda *xs: xs[int(rng.integers(len(xs)))]
     layers = []
     for _ in range(int(rng.integers(3, 7))):
-        mlp = dense(pick(128, 192, 384)) if rng.random() < 0.5 else None
+        mlp = dense(pick(128, 160, 320)) if rng.random() < 0.5 else None
         kind = pick("gla", "mamba2", "attention")
         if kind == "gla":
-            layers.append(gla(heads=pick(1, 2, 4), dim=pick(16, 32, 48, 64), vdim=pick(16, 32, 64),
+            layers.append(gla(heads=pick(1, 2, 4), dim=pick(16, 32, 40, 64), vdim=pick(16, 24, 64),
                               tau=pick(4.0, 8.0, 16.0, 32.0), rank=pick(8, 16, 32), mlp=mlp))
         elif kind == "mamba2":
             heads = pick(2, 4, 8)
@@ -106,8 +106,8 @@ def random_config(seed: int) -> str:
             dim = pick(32, 64, 128)
             layers.append(attention(heads=heads, kv_heads=pick(*[g for g in (1, 2, 4, 8) if heads % g == 0]),
                                     dim=dim, chunk=pick(32, 48, 64, 128), rot=pick(dim // 2, dim),
-                                    base=pick(1e4, 5e4, 1e6), scale=pick(dim ** -0.5, 0.1), mlp=mlp))
-    CONFIGS[name] = config(layers, width=pick(96, 128, 160, 192, 256), vocab=int(rng.integers(200, 700)))
+                                    base=pick(1e4, 2e5, 1e6), scale=pick(dim ** -0.5, 0.1), mlp=mlp))
+    CONFIGS[name] = config(layers, width=pick(96, 128, 160, 224, 256), vocab=int(rng.integers(200, 700)))
     return name
 
 
