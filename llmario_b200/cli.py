@@ -44,8 +44,25 @@ PRESETS = {
 }
 
 
+# Vunasun models of the same sizes (random weights): the width, feed-forward width and attention
+# heads of the Qwen3 preset behind the dash, layers repeating (gla, gla, mamba2, attention).
+VUNASUN_PRESETS = {"vunasun-0.6b": ("qwen3-0.6b", 28), "vunasun-8b": ("qwen3-8b", 36),
+                   "vunasun-tiny": ("tiny-b", 4)}
+
+
+def is_preset(name: str) -> bool:
+    return name.lower() in PRESETS or name.lower() in VUNASUN_PRESETS
+
+
 def preset_config(name: str, num_layers: Optional[int] = None):
     from .config import Qwen3Config
+
+    if name.lower() in VUNASUN_PRESETS:
+        from .benchmarks.vunasun import vunasun_config
+
+        base, layers = VUNASUN_PRESETS[name.lower()]
+        return vunasun_config(PRESETS[base], int(num_layers or layers),
+                              vocab=PRESETS[base]["vocab_size"])
 
     raw = dict(PRESETS[name.lower()], architectures=["Qwen3ForCausalLM"], model_type="qwen3")
     if num_layers:
@@ -58,7 +75,7 @@ def _engine(args, max_requests: int, cache_tokens: Optional[int] = None):
 
     kw = dict(dtype=args.dtype, page_size=args.page_size, token_budget=args.batch,
               max_requests=max_requests, context=args.context, cache_tokens=cache_tokens)
-    if args.model.lower() in PRESETS:
+    if is_preset(args.model):
         return Engine(config=preset_config(args.model, getattr(args, "layers", None)),
                       seed=args.weights_seed, **kw)
     return Engine(args.model, **kw)
@@ -219,7 +236,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                                  "one B200: token ids in, token ids out")
     sub = ap.add_subparsers(dest="cmd", required=True)
     run = sub.add_parser("run", help="generate from a prompt of token ids")
-    run.add_argument("model", help="model folder, or a preset name: " + ", ".join(PRESETS))
+    run.add_argument("model", help="model folder, or a preset name: " + ", ".join(list(PRESETS) + list(VUNASUN_PRESETS)))
     run.add_argument("--tokens", default=None, help="comma-separated prompt token ids")
     run.add_argument("--prompt-len", type=int, default=16,
                      help="without --tokens: this many random ids")

@@ -516,6 +516,12 @@ def test_command_line_and_trace_runner(tmp_path):
         top = np.sort(l)[-2:]
         if top[1] - top[0] > 1e-3 * np.abs(l).max():
             assert tok == int(np.argmax(l))
+    # a preset name gives a model with random weights
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "llmario-b200"), "run", "vunasun-tiny",
+                        "--prompt-len", "5", "--n", "6", "--dtype", "bfloat16", "--page-size", "16",
+                        "--context", "64"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert len(p.stdout.strip().splitlines()[-1].split(",")) == 6
     # the trace runner: two requests, portions beside single tokens, a slot given back and taken
     a, b, c = (tokens_for(name, n, 50 + i) for i, n in enumerate((40, 7, 12)))
     steps = [
