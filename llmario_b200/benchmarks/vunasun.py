@@ -22,24 +22,11 @@ SIZES = {"0.6b": "qwen3-0.6b", "8b": "qwen3-8b"}
 
 def vunasun_config(preset: Dict[str, Any], layers: int, vocab: int = 32768):
     """The Vunasun configuration with the sizes of a Qwen3 preset."""
-    from ..config import VunasunConfig
+    from ..config.vunasun import sized_like
 
-    W, ff = preset["hidden_size"], preset["intermediate_size"]
-    Hq, Hkv, hd = (preset["num_attention_heads"], preset["num_key_value_heads"],
-                   preset["head_dim"])
-    mlp = {"kind": "dense", "ff": ff}
-    gla = {"type": "gla", "mlp": mlp,
-           "mixer": {"heads": max(1, W // 256), "dim": 128, "vdim": 256, "tau": 16.0, "rank": 64}}
-    ssm = {"type": "mamba2", "mlp": mlp,
-           "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4,
-                     "norm_groups": 1}}
-    att = {"type": "attention", "mlp": mlp,
-           "mixer": {"heads": Hq, "kv_heads": Hkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
-                     "mask": {"size": 1024}, "rot": {"dims": hd // 2, "base": 1e6}}}
-    pattern = [gla, gla, ssm, att]
-    return VunasunConfig.from_dict({
-        "architecture": "Vunasun", "vocab": vocab, "width": W, "norm": {"eps": 1e-6},
-        "layers": [pattern[i % 4] for i in range(layers)]})
+    return sized_like(preset["hidden_size"], preset["intermediate_size"],
+                      preset["num_attention_heads"], preset["num_key_value_heads"],
+                      preset["head_dim"], layers, vocab)
 
 
 def _rates(model, page_size: int, batch: int, prompt_len: int, prefill_tokens: int, steps: int,

@@ -58,11 +58,13 @@ def preset_config(name: str, num_layers: Optional[int] = None):
     from .config import Qwen3Config
 
     if name.lower() in VUNASUN_PRESETS:
-        from .benchmarks.vunasun import vunasun_config
+        from .config.vunasun import sized_like
 
         base, layers = VUNASUN_PRESETS[name.lower()]
-        return vunasun_config(PRESETS[base], int(num_layers or layers),
-                              vocab=PRESETS[base]["vocab_size"])
+        p = PRESETS[base]
+        return sized_like(p["hidden_size"], p["intermediate_size"], p["num_attention_heads"],
+                          p["num_key_value_heads"], p["head_dim"], int(num_layers or layers),
+                          p["vocab_size"])
 
     raw = dict(PRESETS[name.lower()], architectures=["Qwen3ForCausalLM"], model_type="qwen3")
     if num_layers:

@@ -226,6 +226,29 @@ class VunasunConfig:
         return spec
 
 
+def sized_like(width: int, ff: int, heads: int, kv_heads: int, head_dim: int, layers: int,
+               vocab: int) -> VunasunConfig:
+    """A configuration for models with random weights at the sizes of a transformer: layers
+    repeating (gla, gla, mamba2, attention), every one with a feed-forward of ``ff``; the linear
+    attention with key channels of half and value channels of the whole width in heads of 128 x
+    256, the state-space mixer with twice the width in heads of 64 over 128 state rows, the
+    attention with the given heads, half of each rotated, in chunks of 1,024."""
+    mlp = {"kind": "dense", "ff": ff}
+    gla = {"type": "gla", "mlp": mlp,
+           "mixer": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "tau": 16.0, "rank": 64}}
+    ssm = {"type": "mamba2", "mlp": mlp,
+           "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4,
+                     "norm_groups": 1}}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+                     "scale": head_dim ** -0.5, "mask": {"size": 1024},
+                     "rot": {"dims": head_dim // 2, "base": 1e6}}}
+    pattern = [gla, gla, ssm, att]
+    return VunasunConfig.from_dict({
+        "architecture": "Vunasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+        "layers": [pattern[i % 4] for i in range(layers)]})
+
+
 def _freeze(v):
     if isinstance(v, dict):
         return {k: _freeze_value(x) for k, x in v.items()}

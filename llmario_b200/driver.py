@@ -188,7 +188,9 @@ _launches = c_int(0)
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
               head_dim: int, scale: float, window: Optional[int]) -> None:
-    """Causal attention of every row of the step over its own request's cached keys, by the
+    """(``window``: None or 0 for every earlier key, a positive number for the last so many, a
+    negative one for the query's own chunk of that many positions: ``kernels.mask_code``.)
+    Causal attention of every row of the step over its own request's cached keys, by the
     kernels the driver chooses: bfloat16 with a head size the tensor-core kernels have goes to
     the decode kernels (single tokens and very short portions, keys split across CTAs and
     merged) and to the tcgen05 kernels (longer portions; over a cache with small pages long
