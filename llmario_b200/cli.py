@@ -50,8 +50,15 @@ VUNASUN_PRESETS = {"vunasun-0.6b": ("qwen3-0.6b", 28), "vunasun-8b": ("qwen3-8b"
                    "vunasun-tiny": ("tiny-b", 4)}
 
 
+# Runidra models of the same sizes (random weights): layers repeating (latent attention + dense,
+# matrix memory + routed experts, latent attention + dense, latent attention + routed experts).
+RUNIDRA_PRESETS = {"runidra-0.6b": ("qwen3-0.6b", 28), "runidra-8b": ("qwen3-8b", 36),
+                   "runidra-tiny": ("tiny-b", 4)}
+
+
 def is_preset(name: str) -> bool:
-    return name.lower() in PRESETS or name.lower() in VUNASUN_PRESETS
+    return name.lower() in PRESETS or name.lower() in VUNASUN_PRESETS \
+        or name.lower() in RUNIDRA_PRESETS
 
 
 def preset_config(name: str, num_layers: Optional[int] = None):
@@ -65,6 +72,15 @@ def preset_config(name: str, num_layers: Optional[int] = None):
         return sized_like(p["hidden_size"], p["intermediate_size"], p["num_attention_heads"],
                           p["num_key_value_heads"], p["head_dim"], int(num_layers or layers),
                           p["vocab_size"])
+
+    if name.lower() in RUNIDRA_PRESETS:
+        from .config.runidra import sized_like as runidra_sized_like
+
+        base, layers = RUNIDRA_PRESETS[name.lower()]
+        p = PRESETS[base]
+        return runidra_sized_like(p["hidden_size"], p["intermediate_size"],
+                                  p["num_attention_heads"], p["head_dim"],
+                                  int(num_layers or layers), p["vocab_size"])
 
     raw = dict(PRESETS[name.lower()], architectures=["Qwen3ForCausalLM"], model_type="qwen3")
     if num_layers:

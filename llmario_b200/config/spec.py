@@ -66,10 +66,16 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
     stored_dtype: str = "bfloat16"
+    # None: one residual stream [rows, hidden].  A number S (1 included): the blocks work on S
+    # residual streams [S, rows, hidden] that all start as the embedding output and are summed
+    # in front of the final norm; every block of such a model must be of a kind that takes them.
+    residual_streams: Optional[int] = None
 
     def validate(self) -> None:
         if not self.layers:
             raise ConfigError("a model needs at least one layer")
+        if self.residual_streams is not None and self.residual_streams < 1:
+            raise ConfigError("residual_streams must be at least 1")
         for i, call in enumerate(self.run_order):
             if not 0 <= call.layer < len(self.layers):
                 raise ConfigError(f"run order entry {i} names layer {call.layer}, "

@@ -5,11 +5,15 @@
 // Keys are visited in tiles of 32 aligned to absolute positions, each lane scoring one key, so
 // the order of every sum depends only on positions: the result for a row is the same however the
 // tokens were cut into steps, whatever else is in the batch and whichever pages hold the keys.
-// Any head size up to 256 (multiples of 8 are read in wide pieces); any number of heads and groups.
+// Any head size up to 640 (multiples of 8 are read in wide pieces); any number of heads and groups.
+// Two options: `sink`, a number per query head that is added to the softmax's sum as exp(sink)
+// (a key that has no value: it takes weight and gives nothing); `vd`, how many of a value
+// row's first channels are summed and written (out is [rows][Hq][vd]; the rest of a value row is
+// not read), for caches whose values are a prefix of their keys.
 #include "common.cuh"
 
 namespace {
-constexpr int MAX_HD = 256;
+constexpr int MAX_HD = 640;
 constexpr int WARPS = 4;
 
 template <typename T> struct Vec8;  // 8 elements of T loaded at once
@@ -35,12 +39,13 @@ template <> struct Vec8<bf16> {
 };
 
 // VEC: the head size is a multiple of 8, so a key row is read in 16-byte (32-byte) pieces.
-template <typename T, bool VEC>
+// NACC: 32-channel pieces of a value row that a lane sums (vd <= 32 * NACC)
+template <typename T, bool VEC, int NACC>
 __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
     const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ k_cache,
     const T* __restrict__ v_cache, long long page_stride, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ row_slot, const int* __restrict__ row_pos, int rows,
-    int Hq, int Hkv, int hd, int page_size, float scale, int window) {
+    int Hq, int Hkv, int hd, int page_size, float scale, int window, const float* __restrict__ sink, int vd) {
   __shared__ float q_s[WARPS][MAX_HD];
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp_in_block;
@@ -57,9 +62,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
   __syncwarp();
 
   float m = -INFINITY, l = 0.f;
-  float acc[MAX_HD / 32];
+  float acc[NACC];
 #pragma unroll
-  for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
+  for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
 
   for (int base = (lo / 32) * 32; base <= pos; base += 32) {
     const int p = base + lane;
@@ -88,7 +93,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
     const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
     l = l * corr + warp_sum(w);
 #pragma unroll
-    for (int i = 0; i < MAX_HD / 32; ++i) acc[i] *= corr;
+    for (int i = 0; i < NACC; ++i) acc[i] *= corr;
     m = m_new;
     const unsigned mask = __ballot_sync(0xffffffffu, valid);
     for (int j = 0; j < 32; ++j) {
@@ -97,18 +102,19 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
       const long long oj = __shfl_sync(0xffffffffu, off, j);
       const T* vr = v_cache + oj;
 #pragma unroll
-      for (int i = 0; i < MAX_HD / 32; ++i) {
+      for (int i = 0; i < NACC; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) acc[i] = fmaf(wj, to_f32(vr[d]), acc[i]);
+        if (d < vd) acc[i] = fmaf(wj, to_f32(vr[d]), acc[i]);
       }
     }
   }
+  if (sink) l += expf(sink[h] - m);     // (m is finite: a row sees at least its own key)
   const float inv = 1.0f / l;
-  T* orow = out + ((size_t)t * Hq + h) * hd;
+  T* orow = out + ((size_t)t * Hq + h) * vd;
 #pragma unroll
-  for (int i = 0; i < MAX_HD / 32; ++i) {
+  for (int i = 0; i < NACC; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) orow[d] = from_f32<T>(acc[i] * inv);
+    if (d < vd) orow[d] = from_f32<T>(acc[i] * inv);
   }
 }
 }  // namespace
@@ -117,24 +123,33 @@ LLM_EXPORT int llm_attention_generic(const void* q, void* out, const void* k_cac
                                      const void* v_cache, int dtype, long long page_stride,
                                      const int* block_table, int table_stride, const int* row_slot,
                                      const int* row_pos, int rows, int Hq, int Hkv, int hd,
-                                     int page_size, float scale, int window, cudaStream_t stream) {
+                                     int page_size, float scale, int window, const float* sink, int vd,
+                                     cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (hd > MAX_HD || hd <= 0 || Hkv <= 0 || Hq % Hkv != 0) return LLM_ERR_UNSUPPORTED;
+  if (vd <= 0) vd = hd;
+  if (hd > MAX_HD || hd <= 0 || vd > hd || Hkv <= 0 || Hq % Hkv != 0) return LLM_ERR_UNSUPPORTED;
   const bool vec = hd % 8 == 0 && (page_stride % 8) == 0 &&
                    (((uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0;
   const long long items = (long long)rows * Hq;
   const int blocks = (int)((items + WARPS - 1) / WARPS);
-#define GENERIC(T, V)                                                                               \
-  attention_generic_kernel<T, V><<<blocks, WARPS * 32, 0, stream>>>(                                \
+#define GENERIC(T, V, N)                                                                            \
+  attention_generic_kernel<T, V, N><<<blocks, WARPS * 32, 0, stream>>>(                             \
       (const T*)q, (T*)out, (const T*)k_cache, (const T*)v_cache, page_stride, block_table,         \
-      table_stride, row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window)
+      table_stride, row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window, sink, vd)
+#define GENERIC_N(T, V)                                  \
+  do {                                                   \
+    if (vd <= 128) GENERIC(T, V, 4);                     \
+    else if (vd <= 256) GENERIC(T, V, 8);                \
+    else GENERIC(T, V, MAX_HD / 32);                     \
+  } while (0)
   if (dtype == LLM_F32) {
-    if (vec) GENERIC(float, true); else GENERIC(float, false);
+    if (vec) GENERIC_N(float, true); else GENERIC_N(float, false);
   } else if (dtype == LLM_BF16) {
-    if (vec) GENERIC(bf16, true); else GENERIC(bf16, false);
+    if (vec) GENERIC_N(bf16, true); else GENERIC_N(bf16, false);
   } else {
     return LLM_ERR_UNSUPPORTED;
   }
+#undef GENERIC_N
 #undef GENERIC
   return launch_status();
 }

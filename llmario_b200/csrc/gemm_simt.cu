@@ -11,7 +11,11 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 template <typename TA, typename TW, typename TC, bool ACCUMULATE>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
                                                         TC* __restrict__ C, int M, int N, int K,
-                                                        int lda, int ldw, int ldc) {
+                                                        int lda, int ldw, int ldc, long long a_batch,
+                                                        long long w_batch, long long c_batch) {
+  // blockIdx.z: one of several independent products (a head of a per-head map), operands a
+  // fixed number of elements apart
+  A += (size_t)blockIdx.z * a_batch, W += (size_t)blockIdx.z * w_batch, C += (size_t)blockIdx.z * c_batch;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -67,12 +71,15 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A
 
 template <typename TA, typename TW, typename TC>
 int launch(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
-           int accumulate, cudaStream_t s) {
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+           int accumulate, cudaStream_t s, int batch = 1, long long a_batch = 0, long long w_batch = 0,
+           long long c_batch = 0) {
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
   if (accumulate)
-    gemm_simt_kernel<TA, TW, TC, true><<<grid, 256, 0, s>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+    gemm_simt_kernel<TA, TW, TC, true><<<grid, 256, 0, s>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw,
+                                                            ldc, a_batch, w_batch, c_batch);
   else
-    gemm_simt_kernel<TA, TW, TC, false><<<grid, 256, 0, s>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+    gemm_simt_kernel<TA, TW, TC, false><<<grid, 256, 0, s>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw,
+                                                             ldc, a_batch, w_batch, c_batch);
   return launch_status();
 }
 }  // namespace
@@ -91,6 +98,22 @@ LLM_EXPORT int llm_gemm_simt(const void* A, int a_dtype, const void* W, int w_dt
   if (a_dtype == LLM_BF16 && w_dtype == LLM_F32 && c_dtype == LLM_F32) GO(bf16, float, float);
   if (a_dtype == LLM_BF16 && w_dtype == LLM_F32 && c_dtype == LLM_BF16) GO(bf16, float, bf16);
   if (a_dtype == LLM_F32 && w_dtype == LLM_BF16 && c_dtype == LLM_F32) GO(float, bf16, float);
+#undef GO
+  return LLM_ERR_UNSUPPORTED;
+}
+
+// `batch` independent products of the same sizes in one launch: product b reads A + b * a_batch
+// and W + b * w_batch and writes C + b * c_batch (elements).  Operands and result of one type.
+LLM_EXPORT int llm_gemm_simt_batched(const void* A, const void* W, void* C, int dtype, int c_dtype, int M, int N,
+                                     int K, int lda, int ldw, int ldc, int batch, long long a_batch,
+                                     long long w_batch, long long c_batch, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0 || batch > 65535) return LLM_ERR_ARGUMENT;
+#define GO(TA, TW, TC) \
+  return launch<TA, TW, TC>(A, W, C, M, N, K, lda, ldw, ldc, 0, stream, batch, a_batch, w_batch, c_batch)
+  if (dtype == LLM_F32 && c_dtype == LLM_F32) GO(float, float, float);
+  if (dtype == LLM_BF16 && c_dtype == LLM_F32) GO(bf16, bf16, float);
+  if (dtype == LLM_BF16 && c_dtype == LLM_BF16) GO(bf16, bf16, bf16);
 #undef GO
   return LLM_ERR_UNSUPPORTED;
 }

@@ -1,0 +1,182 @@
+// A feed-forward of routed experts.  Per token the router's logits choose `top` of E small gated
+// feed-forwards; their outputs are summed with the softmax of the chosen logits as weights.
+//   route:    ids[r][k], wts[r][k]  from  z[r][0:E]                      (32-bit)
+//   gate/up:  act[r][k][f] = silu(Wg_e[f] . h_r) * (Wu_e[f] . h_r),  e = ids[r][k]
+//   down:     y[r][c] (+)= sum_k wts[r][k] * (Wd_e[c] . act[r][k])  [+ sigmoid(g_r) * shared[r][c]]
+// The row-wise kernels here give every (token, chosen expert) its own matrix-vector products:
+// the form for steps of few rows, where a token's experts are read once each and nothing has
+// to be sorted; which expert a row uses is read on the device, so recorded steps replay.
+// Sums run in a fixed order per output, so a row's result does not depend on the batch.
+#include "common.cuh"
+
+namespace {
+constexpr int MAX_TOP = 16;
+
+// One warp per row.  The k-th choice is the largest logit not chosen before (the lowest index
+// among equals); weights are the softmax over the chosen logits only.
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, int z_stride, int rows, int E,
+                                                        int top, int* __restrict__ ids, float* __restrict__ wts) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const float* zr = z + (size_t)r * z_stride;
+  float best[MAX_TOP];
+  int pick[MAX_TOP];
+  for (int k = 0; k < top; ++k) {
+    float v = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= pick[j] == e;
+      const float x = zr[e];
+      if (!taken && (x > v || (x == v && e < at) || at == 0x7fffffff)) v = x, at = e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (oa != 0x7fffffff && (at == 0x7fffffff || ov > v || (ov == v && oa < at))) v = ov, at = oa;
+    }
+    best[k] = v, pick[k] = at;
+  }
+  if (lane == 0) {
+    float sum = 0.f;       // best[0] is the largest
+    for (int k = 0; k < top; ++k) sum += expf(best[k] - best[0]);
+    for (int k = 0; k < top; ++k) {
+      ids[(size_t)r * top + k] = pick[k];
+      wts[(size_t)r * top + k] = expf(best[k] - best[0]) / sum;
+    }
+  }
+}
+
+template <typename T> __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x,
+                                                               int n, int lane);
+template <> __device__ __forceinline__ float dot_row<float>(const float* __restrict__ w, const float* __restrict__ x,
+                                                            int n, int lane) {
+  float acc = 0.f;
+  for (int i = lane; i < n; i += 32) acc = fmaf(w[i], x[i], acc);
+  return warp_sum(acc);
+}
+template <> __device__ __forceinline__ float dot_row<bf16>(const bf16* __restrict__ w, const float* __restrict__ x,
+                                                           int n, int lane) {
+  float acc = 0.f;
+  if ((n & 7) == 0 && ((uintptr_t)w & 15) == 0) {
+    for (int i = lane * 8; i < n; i += 256) {
+      const uint4 a = *reinterpret_cast<const uint4*>(w + i);
+      const uint32_t u[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc = fmaf(__uint_as_float(u[j] << 16), x[i + 2 * j], acc);
+        acc = fmaf(__uint_as_float(u[j] & 0xffff0000u), x[i + 2 * j + 1], acc);
+      }
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) acc = fmaf(__bfloat162float(w[i]), x[i], acc);
+  }
+  return warp_sum(acc);
+}
+
+// grid (rows * top, ff tiles of 8); a block stages its row of h in shared memory, a warp makes
+// two features.  gate_up: [E][2 ff][width], gate rows first.
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gate_up_rows_kernel(const T* __restrict__ h, const T* __restrict__ gate_up,
+                                                               const int* __restrict__ ids, T* __restrict__ act,
+                                                               int width, int ff, int top) {
+  extern __shared__ float h_s[];
+  pdl_trigger();
+  pdl_wait();
+  const int item = blockIdx.x, r = item / top;
+  const int e = ids[item];
+  for (int i = threadIdx.x; i < width; i += blockDim.x) h_s[i] = to_f32(h[(size_t)r * width + i]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* we = gate_up + (size_t)e * 2 * ff * width;
+  for (int f = blockIdx.y * 8 + warp; f < min(ff, blockIdx.y * 8 + 8); f += 4) {
+    const float g = dot_row<T>(we + (size_t)f * width, h_s, width, lane);
+    const float u = dot_row<T>(we + (size_t)(ff + f) * width, h_s, width, lane);
+    if (lane == 0) act[(size_t)item * ff + f] = from_f32<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+// grid (rows, width tiles of 8); a block stages its row's `top` activation vectors, a warp makes two
+// output channels.  down: [E][width][ff].
+template <typename T>
+__global__ void __launch_bounds__(128) moe_down_rows_kernel(const T* __restrict__ act, const T* __restrict__ down,
+                                                            const int* __restrict__ ids, const float* __restrict__ wts,
+                                                            const float* __restrict__ shared, const float* __restrict__ gate,
+                                                            int gate_stride, float* __restrict__ y, int width, int ff,
+                                                            int top, int accumulate) {
+  extern __shared__ float a_s[];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) a_s[i] = to_f32(act[(size_t)r * top * ff + i]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = blockIdx.y * 8 + warp; c < min(width, blockIdx.y * 8 + 8); c += 4) {
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int e = ids[(size_t)r * top + k];
+      const float d = dot_row<T>(down + ((size_t)e * width + c) * ff, a_s + (size_t)k * ff, ff, lane);
+      sum = fmaf(wts[(size_t)r * top + k], d, sum);
+    }
+    if (lane == 0) {
+      if (shared) sum = fmaf(1.f / (1.f + expf(-gate[(size_t)r * gate_stride])), shared[(size_t)r * width + c], sum);
+      float* dst = y + (size_t)r * width + c;
+      *dst = accumulate ? *dst + sum : sum;
+    }
+  }
+}
+}  // namespace
+
+LLM_EXPORT int llm_moe_route(const float* z, int z_stride, int rows, int E, int top, int* ids, float* wts,
+                             cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (top < 1 || top > MAX_TOP || top > E) return LLM_ERR_UNSUPPORTED;
+  return launch_pdl(moe_route_kernel, (rows + 3) / 4, 128, 0, stream, z, z_stride, rows, E, top, ids, wts);
+}
+
+LLM_EXPORT int llm_moe_gate_up_rows(const void* h, const void* gate_up, const int* ids, void* act, int dtype,
+                                    int rows, int width, int ff, int top, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((ff + 7) / 8 > 65535 || (size_t)width * 4 > 200 * 1024) return LLM_ERR_UNSUPPORTED;
+  const dim3 grid(rows * top, (ff + 7) / 8);
+  const size_t smem = (size_t)width * 4;
+  if (dtype == LLM_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(moe_gate_up_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl(moe_gate_up_rows_kernel<float>, grid, 128, smem, stream, (const float*)h,
+                      (const float*)gate_up, ids, (float*)act, width, ff, top);
+  }
+  if (dtype == LLM_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(moe_gate_up_rows_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl(moe_gate_up_rows_kernel<bf16>, grid, 128, smem, stream, (const bf16*)h, (const bf16*)gate_up,
+                      ids, (bf16*)act, width, ff, top);
+  }
+  return LLM_ERR_UNSUPPORTED;
+}
+
+LLM_EXPORT int llm_moe_down_rows(const void* act, const void* down, const int* ids, const float* wts,
+                                 const float* shared, const float* gate, int gate_stride, float* y, int dtype,
+                                 int rows, int width, int ff, int top, int accumulate, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const size_t smem = (size_t)top * ff * 4;
+  if ((width + 7) / 8 > 65535 || smem > 200 * 1024) return LLM_ERR_UNSUPPORTED;
+  if (shared && !gate) return LLM_ERR_ARGUMENT;
+  const dim3 grid(rows, (width + 7) / 8);
+  if (dtype == LLM_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(moe_down_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl(moe_down_rows_kernel<float>, grid, 128, smem, stream, (const float*)act, (const float*)down,
+                      ids, wts, shared, gate, gate_stride, y, width, ff, top, accumulate);
+  }
+  if (dtype == LLM_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(moe_down_rows_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl(moe_down_rows_kernel<bf16>, grid, 128, smem, stream, (const bf16*)act, (const bf16*)down, ids,
+                      wts, shared, gate, gate_stride, y, width, ff, top, accumulate);
+  }
+  return LLM_ERR_UNSUPPORTED;
+}

@@ -52,6 +52,8 @@ enum DecayKind : int {
   DECAY_SIGMOID_POW = 1,   // a = sigmoid(d)^c            d per (row, head, key channel), c a constant
   DECAY_RATE_STEP = 2,     // step = softplus(d + p1[h]); a = exp(-exp(p0[h]) * step); v is scaled by step
                            //                             d per (row, head)
+  DECAY_SCALAR_INPUT = 3,  // a = d, v is scaled by d2    d, d2 per (row, head): a decay and an input
+                           //                             weight that another kernel has made
 };
 
 struct ScanArgs {
@@ -59,6 +61,10 @@ struct ScanArgs {
   const float* k; int k_stride;          // k[row * k_stride + g * K + i]
   const float* v; int v_stride;          // v[row * v_stride + h * V + j]
   const float* d; int d_stride;          // the decay's argument (see DecayKind)
+  const float* d2;                       // DECAY_SCALAR_INPUT: the input weight, strided as d
+  int v_cols;                            // value channels of a head in v: V, or V - 1 when the last
+                                         // state column is fed the constant 1 (`ones`)
+  int ones;
   const float* p0; const float* p1;      // per-head constants of DECAY_RATE_STEP
   float c;                               // the exponent of DECAY_SIGMOID_POW
   float q_scale;                         // q is multiplied by it (applied to the head's output: the same product)
@@ -101,6 +107,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
   __shared__ __align__(16) float a_s[2][VEC ? TC : 1][VEC ? KP : 4];
   __shared__ __align__(16) float v_s[2][TC][COLS];
   __shared__ float d_s[2][TC];          // scalar decay: its argument, then the decay itself
+  __shared__ float w_s[2][TC];          // DECAY_SCALAR_INPUT: the input weight
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -155,12 +162,16 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
     }
     for (int idx = tid; idx < n_tok * COLS; idx += SCAN_THREADS) {
       const int tt = idx / COLS, cc = idx - tt * COLS;
-      if (j0 + cc < V) cp_async4(&v_s[st][tt][cc], a.v + (size_t)(t0 + tt) * a.v_stride + h * V + j0 + cc);
-      else v_s[st][tt][cc] = 0.f;
+      if (j0 + cc < a.v_cols)
+        cp_async4(&v_s[st][tt][cc], a.v + (size_t)(t0 + tt) * a.v_stride + h * a.v_cols + j0 + cc);
+      else
+        v_s[st][tt][cc] = (a.ones && j0 + cc == V - 1) ? 1.f : 0.f;
     }
     if (!VEC)
-      for (int tt = tid; tt < n_tok; tt += SCAN_THREADS)
+      for (int tt = tid; tt < n_tok; tt += SCAN_THREADS) {
         cp_async4(&d_s[st][tt], a.d + (size_t)(t0 + tt) * a.d_stride + h);
+        if (a.kind == DECAY_SCALAR_INPUT) cp_async4(&w_s[st][tt], a.d2 + (size_t)(t0 + tt) * a.d_stride + h);
+      }
     cp_async_commit();
   };
 
@@ -207,6 +218,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
           // sigmoid(d)^c = exp(c * log sigmoid(d)), log sigmoid(d) = -softplus(-d)
           a_s[st][tt][i] = expf(-a.c * softplus_f(-a_s[st][tt][i]));
         }
+    } else if (a.kind == DECAY_SCALAR_INPUT) {
+      for (int idx = tid; idx < n_tok * COLS; idx += SCAN_THREADS) {
+        const int tt = idx / COLS, cc = idx - tt * COLS;
+        v_s[st][tt][cc] *= w_s[st][tt];
+      }
     } else {
       for (int idx = tid; idx < n_tok * COLS; idx += SCAN_THREADS) {
         const int tt = idx / COLS, cc = idx - tt * COLS;
@@ -273,7 +289,7 @@ template <int L, int NF>
 int launch_scan(const ScanArgs& a, int blocks_x, cudaStream_t stream) {
   constexpr int COLS = 4 * (32 / L) * (SCAN_THREADS / 32);
   const dim3 grid(blocks_x, a.H, (a.V + COLS - 1) / COLS);
-  if (a.kind == DECAY_RATE_STEP)
+  if (a.kind == DECAY_RATE_STEP || a.kind == DECAY_SCALAR_INPUT)
     return launch_pdl(linear_recurrence_kernel<L, NF, false>, grid, SCAN_THREADS, 0, stream, a);
   return launch_pdl(linear_recurrence_kernel<L, NF, true>, grid, SCAN_THREADS, 0, stream, a);
 }
@@ -514,7 +530,118 @@ __global__ void __launch_bounds__(THREADS) gated_group_norm_vec_kernel(
     store(c0 + 4 * i, v, gt, scale);
   }
 }
+
+// ---- exponential gates kept in range by a running maximum (the gates of a matrix memory)
+//   i_t = cap tanh((zi_t + bi) / cap),  f_t = log sigmoid(cap tanh((zf_t + bf) / cap))
+//   m_t = max(f_t + m_{t-1}, i_t),  keep_t = exp(f_t + m_{t-1} - m_t),  take_t = exp(i_t - m_t)
+// per (request, head); m is carried in the request's state slot and starts at 0.  One warp per
+// (request of the step, head): the lanes make i and f of 32 tokens at a time, then the chain of
+// maxima is walked token by token (every lane walks it; lane j keeps what belongs to token j), so
+// the result is that of the token-by-token recurrence however the prompt was cut.
+// out[row][0:H] = keep, [H:2H] = take, [2H:3H] = m.
+__device__ __forceinline__ float log_sigmoid_f(float z) { return -softplus_f(-z); }
+__global__ void __launch_bounds__(32) log_gate_scan_kernel(
+    const float* __restrict__ zi, const float* __restrict__ zf, int z_stride, const float* __restrict__ bi,
+    const float* __restrict__ bf, float cap, float* __restrict__ m_state, long long state_stride,
+    float* __restrict__ out, int out_stride, const int* __restrict__ seg, const int* __restrict__ row_slot,
+    int single, int H) {
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.y, lane = threadIdx.x;
+  int slot, first, end;
+  if (single) {
+    first = blockIdx.x, end = first + 1, slot = row_slot[first];
+  } else {
+    slot = seg[SEG * blockIdx.x + 2];
+    if (slot < 0) return;
+    first = seg[SEG * slot], end = seg[SEG * slot + 1];
+  }
+  if (end <= first) return;
+  float* mp = m_state + (size_t)slot * state_stride + h;
+  float m = *mp;
+  const float b_i = bi ? bi[h] : 0.f, b_f = bf ? bf[h] : 0.f;
+  for (int t0 = first; t0 < end; t0 += 32) {
+    const int t = t0 + lane, n = min(32, end - t0);
+    float gi = 0.f, gf = 0.f;
+    if (t < end) {
+      const float a = zi[(size_t)t * z_stride + h] + b_i, b = zf[(size_t)t * z_stride + h] + b_f;
+      gi = cap > 0.f ? cap * tanhf(a / cap) : a;
+      gf = log_sigmoid_f(cap > 0.f ? cap * tanhf(b / cap) : b);
+    }
+    float m_before = m, m_mine = m;
+    for (int j = 0; j < n; ++j) {
+      const float fj = __shfl_sync(0xffffffffu, gf, j), ij = __shfl_sync(0xffffffffu, gi, j);
+      const float m_new = fmaxf(fj + m, ij);
+      if (j == lane) m_before = m, m_mine = m_new;
+      m = m_new;
+    }
+    if (t < end) {
+      float* o = out + (size_t)t * out_stride + h;
+      o[0] = expf(gf + m_before - m_mine);
+      o[H] = expf(gi - m_mine);
+      o[2 * H] = m_mine;
+    }
+  }
+  if (lane == 0) *mp = m;
+}
+
+// ---- the output of a matrix memory: normaliser, unit norm per head, gain, sigmoid gate
+//   y = o / (max(|z|, exp(-m)) + floor);  out = y / rms(y) * w * sigmoid(g)
+// o[row][h][0:V] is the memory's answer and o[row][h][V] = z its normaliser's (both from the
+// recurrence above, whose last state column was fed ones); m[row][h] the running maximum of the
+// gates.  One warp per (row, head); w has a gain per channel of every head.
+template <typename TOut>
+__global__ void __launch_bounds__(128) memory_out_norm_kernel(
+    const float* __restrict__ o, int o_stride, const float* __restrict__ m, int m_stride,
+    const float* __restrict__ g, int g_stride, const float* __restrict__ w, TOut* __restrict__ out,
+    int out_stride, long long items, int H, int V, float eps, float floor_) {
+  pdl_trigger();
+  pdl_wait();
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const int r = (int)(item / H), h = (int)(item % H);
+  const float* orow = o + (size_t)r * o_stride + (size_t)h * (V + 1);
+  const float den = fmaxf(fabsf(orow[V]), expf(-m[(size_t)r * m_stride + h])) + floor_;
+  float ss = 0.f;
+  for (int j = lane; j < V; j += 32) {
+    const float y = orow[j] / den;
+    ss = fmaf(y, y, ss);
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)V + eps);
+  for (int j = lane; j < V; j += 32) {
+    const int ch = h * V + j;
+    const float gate = 1.f / (1.f + expf(-g[(size_t)r * g_stride + ch]));
+    out[(size_t)r * out_stride + ch] = from_f32<TOut>(orow[j] / den * scale * w[ch] * gate);
+  }
+}
 }  // namespace
+
+LLM_EXPORT int llm_log_gate_scan(const float* zi, const float* zf, int z_stride, const float* bi,
+                                 const float* bf, float cap, float* m_state, long long state_stride,
+                                 float* out, int out_stride, const int* seg, const int* row_slot, int rows,
+                                 int n_requests, int single, int H, cudaStream_t stream) {
+  if (rows <= 0 || H <= 0) return 0;
+  if (!single && (!seg || n_requests <= 0)) return LLM_ERR_ARGUMENT;
+  return launch_pdl(log_gate_scan_kernel, dim3(single ? rows : n_requests, H), 32, 0, stream, zi, zf, z_stride,
+                    bi, bf, cap, m_state, state_stride, out, out_stride, seg, row_slot, single, H);
+}
+
+LLM_EXPORT int llm_memory_out_norm(const float* o, int o_stride, const float* m, int m_stride, const float* g,
+                                   int g_stride, const float* w, void* out, int out_dtype, int out_stride,
+                                   int rows, int H, int V, float eps, float floor_, cudaStream_t stream) {
+  const long long items = (long long)rows * H;
+  if (items <= 0 || V <= 0) return 0;
+  const int blocks = (int)((items + 3) / 4);
+  if (out_dtype == LLM_F32)
+    return launch_pdl(memory_out_norm_kernel<float>, blocks, 128, 0, stream, o, o_stride, m, m_stride, g,
+                      g_stride, w, (float*)out, out_stride, items, H, V, eps, floor_);
+  if (out_dtype == LLM_BF16)
+    return launch_pdl(memory_out_norm_kernel<bf16>, blocks, 128, 0, stream, o, o_stride, m, m_stride, g,
+                      g_stride, w, (bf16*)out, out_stride, items, H, V, eps, floor_);
+  return LLM_ERR_UNSUPPORTED;
+}
 
 LLM_EXPORT int llm_segment_table(const int* row_slot, int rows, int* seg, int n_slots, cudaStream_t stream) {
   if (n_slots <= 0) return 0;
@@ -524,21 +651,26 @@ LLM_EXPORT int llm_segment_table(const int* row_slot, int rows, int* seg, int n_
 // The recurrence over the rows of a step (see the top of this file).  `single`: every row is a
 // request of its own; else `seg` is the table of llm_segment_table and `n_requests` the number of
 // requests that have rows in the step.  The state of a (slot, head) is V x K floats, the key
-// channel fastest.
+// channel fastest.  `ones`: v has V - 1 channels per head and the state's last column is fed the
+// constant 1, so that it holds the decayed sum of the keys alone and the last output channel is
+// its product with the query (the normaliser of a matrix memory).
 LLM_EXPORT int llm_linear_recurrence(const float* q, int q_stride, const float* k, int k_stride, const float* v,
-                                     int v_stride, const float* d, int d_stride, const float* p0,
-                                     const float* p1, float c, float q_scale, float* state,
+                                     int v_stride, const float* d, int d_stride, const float* d2, int ones,
+                                     const float* p0, const float* p1, float c, float q_scale, float* state,
                                      long long state_stride, float* out, int out_stride, const int* seg,
                                      const int* row_slot, int rows, int n_requests, int single, int H, int G,
                                      int K, int V, int kind, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || kind < 0 || kind > 2) return LLM_ERR_ARGUMENT;
+  if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || kind < 0 || kind > 3) return LLM_ERR_ARGUMENT;
   if (kind == DECAY_RATE_STEP && (!p0 || !p1)) return LLM_ERR_ARGUMENT;
+  if (kind == DECAY_SCALAR_INPUT && !d2) return LLM_ERR_ARGUMENT;
+  if (ones && V < 2) return LLM_ERR_ARGUMENT;
   if (!single && (!seg || n_requests <= 0)) return LLM_ERR_ARGUMENT;
   if (K > 512) return LLM_ERR_UNSUPPORTED;     // (sixty-four state registers per lane are the most)
   ScanArgs a;
   a.q = q, a.q_stride = q_stride, a.k = k, a.k_stride = k_stride, a.v = v, a.v_stride = v_stride;
   a.d = d, a.d_stride = d_stride, a.p0 = p0, a.p1 = p1, a.c = c, a.q_scale = q_scale;
+  a.d2 = d2, a.ones = ones ? 1 : 0, a.v_cols = ones ? V - 1 : V;
   a.state = state, a.state_stride = state_stride, a.out = out, a.out_stride = out_stride;
   a.seg = seg, a.row_slot = row_slot;
   a.single = single, a.H = H, a.G = G, a.K = K, a.V = V, a.kind = kind;

@@ -50,7 +50,8 @@ int llm_rope_table(const int* row_pos, const float* inv_freq, float* cos_sin, in
 int llm_attention_generic(const void* q, void* out, const void* k_cache, const void* v_cache, int dtype,
                           long long page_stride, const int* block_table, int table_stride,
                           const int* row_slot, const int* row_pos, int rows, int Hq, int Hkv, int hd,
-                          int page_size, float scale, int window, cudaStream_t stream);
+                          int page_size, float scale, int window, const float* sink, int vd,
+                          cudaStream_t stream);
 int llm_attention_flash(const void* q, void* out, float* part_o, float* part_ml, const void* k_cache,
                         const void* v_cache, long long page_stride, const int* block_table, int table_stride,
                         const int* items, const int* row_slot, const int* row_pos, int n_items,
@@ -500,10 +501,12 @@ struct Run {
   int attention(const LlmLayerDesc& L, const LlmCallDesc& c, const void* q, void* out) {
     const int Hq = L.num_heads, Hkv = L.num_kv_heads, hd = L.head_dim, group = Hq / Hkv;
     const int window = L.window;
-    if (st.dtype != LLM_BF16 || !(hd == 32 || hd == 64 || hd == 128) || group > 16)
+    // (a sink in the softmax's sum, or values that are a prefix of their keys: the generic kernel)
+    const bool plain = L.sink == nullptr && (L.value_dim == 0 || L.value_dim == hd);
+    if (!plain || st.dtype != LLM_BF16 || !(hd == 32 || hd == 64 || hd == 128) || group > 16)
       return check(llm_attention_generic(q, out, c.k, c.v, st.dtype, c.page_stride, c.block_table,
                                          c.table_stride, st.row_slot, st.row_pos, st.rows, Hq, Hkv, hd,
-                                         c.page_size, L.scale, window, stream), K_GENERIC);
+                                         c.page_size, L.scale, window, L.sink, L.value_dim, stream), K_GENERIC);
     const int ps = c.page_size;
     const bool tc = (hd == 64 || hd == 128) && 128 % group == 0 && (c.page_stride * 2) % 16 == 0;
     const bool x2 = tc && ps >= 32 && (ps & (ps - 1)) == 0 && c.storage != nullptr && ps < 64 &&

@@ -18,7 +18,8 @@ struct LlmLayerDesc {
   int w_qkv_dtype, w_o_dtype, w_gate_up_dtype, w_down_dtype;
   float scale, attn_factor;
   float mixer_norm_eps, ffn_norm_eps, qk_norm_eps;
-  float pad_;
+  int value_dim;           // 0 or head_dim: whole value rows; less: only a value row's first channels are summed
+                           // and written (the output is [rows][heads][value_dim])
   const float* mixer_norm_w;
   const float* ffn_norm_w;
   const float* q_norm_w;   // null: no per-head norm
@@ -28,6 +29,7 @@ struct LlmLayerDesc {
   const void* w_o;         // [hidden][heads * head_dim]
   const void* w_gate_up;   // [2 * intermediate][hidden]
   const void* w_down;      // [hidden][intermediate]
+  const float* sink;       // null, or a number per query head added to the softmax's sum as exp(sink)
 };
 
 // One run-order entry: which layer, and where its keys and values live.

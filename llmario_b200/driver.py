@@ -28,10 +28,11 @@ class LayerDesc(Structure):
                 ("w_qkv_dtype", c_int), ("w_o_dtype", c_int), ("w_gate_up_dtype", c_int),
                 ("w_down_dtype", c_int),
                 ("scale", c_float), ("attn_factor", c_float), ("mixer_norm_eps", c_float),
-                ("ffn_norm_eps", c_float), ("qk_norm_eps", c_float), ("pad_", c_float),
+                ("ffn_norm_eps", c_float), ("qk_norm_eps", c_float), ("value_dim", c_int),
                 ("mixer_norm_w", c_void_p), ("ffn_norm_w", c_void_p), ("q_norm_w", c_void_p),
                 ("k_norm_w", c_void_p), ("inv_freq", c_void_p), ("w_qkv", c_void_p),
-                ("w_o", c_void_p), ("w_gate_up", c_void_p), ("w_down", c_void_p)]
+                ("w_o", c_void_p), ("w_gate_up", c_void_p), ("w_down", c_void_p),
+                ("sink", c_void_p)]
 
 
 class CallDesc(Structure):
@@ -187,7 +188,8 @@ _launches = c_int(0)
 
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
-              head_dim: int, scale: float, window: Optional[int]) -> None:
+              head_dim: int, scale: float, window: Optional[int],
+              sink: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> None:
     """(``window``: None or 0 for every earlier key, a positive number for the last so many, a
     negative one for the query's own chunk of that many positions: ``kernels.mask_code``.)
     Causal attention of every row of the step over its own request's cached keys, by the
@@ -195,12 +197,19 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
     the decode kernels (single tokens and very short portions, keys split across CTAs and
     merged) and to the tcgen05 kernels (longer portions; over a cache with small pages long
     portions read a gathered copy of their keys); everything else (32-bit, other head sizes,
-    very large groups) to the generic kernel."""
+    very large groups) to the generic kernel.  ``sink`` (float32, one number per query head)
+    joins the softmax's sum as ``exp(sink)`` without a value; ``value_dim`` says that only the
+    first so many channels of a value row count (``out`` is then ``[rows, heads * value_dim]``)."""
     kernels._cuda(q, out, view.k, view.v, view.block_table)
     assert q.dtype == out.dtype and q.is_contiguous() and out.is_contiguous()
     layer = LayerDesc()
     layer.num_heads, layer.num_kv_heads, layer.head_dim = num_heads, num_kv_heads, head_dim
     layer.scale, layer.window = scale, int(window or 0)
+    layer.value_dim = int(value_dim or 0)
+    if sink is not None:
+        kernels._cuda(sink)
+        assert sink.dtype == torch.float32 and sink.numel() == num_heads
+        layer.sink = sink.data_ptr()
     call = CallDesc()
     fill_call(call, 0, True, view)
     rc = _lib().llm_attention_step(ctypes.byref(layer), ctypes.byref(call),

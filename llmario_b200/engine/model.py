@@ -45,6 +45,17 @@ class Model:
                        for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, weights, dtype, self.device)
         self.head = build_part("head", spec.head, weights, dtype, self.device)
+        if spec.residual_streams is not None:
+            # blocks that work on several residual streams say how many; the sum of the streams
+            # is fused with an RMS norm in front of the head
+            for i, b in enumerate(self.blocks):
+                if getattr(b, "streams", None) != spec.residual_streams:
+                    raise ValueError(f"layer {i}: a model with {spec.residual_streams} residual "
+                                     f"streams needs blocks that take them, not "
+                                     f"{type(b).__name__}")
+            if not (hasattr(self.final_norm, "weight") and hasattr(self.final_norm, "eps")):
+                raise ValueError("a model with residual streams needs an RMS norm as its final "
+                                 "norm")
         # Cache entries.  Every block says what it keeps between steps as a list of needs; each
         # need of each run-order entry gets an entry of its own in the cache manager.  A call
         # that reads another call's cache uses that call's entries, need by need.

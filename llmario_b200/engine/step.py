@@ -100,6 +100,7 @@ class ModelRunner:
                          "graphs_recorded": 0, "graph_replays": 0, "failed_launches": 0,
                          "h2d_bytes": 0}
         self._carried_updates: Optional[List[np.ndarray]] = None   # of a step that failed
+        self._stream_ones: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ requests
     def open(self, request: Any) -> None:
@@ -350,8 +351,15 @@ class ModelRunner:
         """Embedding, every layer call of the run order, final norm and head at the wanted
         rows.  Returns a view of a workspace buffer: read it before the next step."""
         m = self.model
-        x = ctx.buffer("x", (ctx.rows, m.hidden_size), torch.float32)
-        m.embedding.forward(ctx, ctx.tokens, x)
+        streams = m.spec.residual_streams
+        if streams is None:
+            x = ctx.buffer("x", (ctx.rows, m.hidden_size), torch.float32)
+            m.embedding.forward(ctx, ctx.tokens, x)
+        else:
+            # several residual streams, all equal to the embedding output at the start
+            x = ctx.buffer("x", (streams, ctx.rows, m.hidden_size), torch.float32)
+            m.embedding.forward(ctx, ctx.tokens, x[0])
+            kernels.stream_fill(x)
         nat = self.native
         if nat is not None:
             nat.begin_step(ctx, x)
@@ -365,11 +373,26 @@ class ModelRunner:
                 m.blocks[calls[i].layer].forward(ctx, calls[i], x)
                 i += 1
         logits = ctx.buffer("logits", (n_want, m.vocab_size), torch.float32)
+        if streams is not None:
+            # the write of the last sublayer, which its block left to whoever comes next
+            write = ctx.shared.pop("streams.pending", None)
+            if write:
+                kernels.stream_step(x, **write)
         if n_want:
             hsel = ctx.buffer("head.h", (n_want, m.hidden_size))
-            m.final_norm.apply(ctx, x, hsel, want_dev)
+            if streams is None:
+                m.final_norm.apply(ctx, x, hsel, want_dev)
+            else:
+                # the sum of the streams and the final norm, at the wanted rows only
+                kernels.stream_step(x, in_coef=self._ones(streams), weight=m.final_norm.weight,
+                                    eps=m.final_norm.eps, out=hsel, rows_index=want_dev)
             m.head.forward(ctx, hsel, logits)
         return logits
+
+    def _ones(self, n: int) -> torch.Tensor:
+        if self._stream_ones is None or self._stream_ones.numel() != n:
+            self._stream_ones = torch.ones(n, dtype=torch.float32, device=self.device)
+        return self._stream_ones
 
     def _graph_step(self, key, forward) -> torch.Tensor:
         """Run ``forward`` eagerly the first time a key is seen, record it the second time,

@@ -51,7 +51,7 @@ def _signatures():
         "llm_qk_norm_rope_store": [P, I, P, P, P, I, L, P, I, P, P, P, P, P, P, F, I, I, I, I, I,
                                    I, F, I, I, I, P],
         "llm_rope_table": [P, P, P, I, I, F, P],
-        "llm_attention_generic": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P],
+        "llm_attention_generic": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P, I, P],
         "llm_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P],
         "llm_gemv_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, P],
         "llm_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
@@ -75,8 +75,20 @@ def _signatures():
         "llm_head_gate": [P, I, P, I, I, I, I, I, P],
         "llm_segment_table": [P, I, P, I, P],
         "llm_bias_sigmoid_pow": [P, P, I, I, F, P],
-        "llm_linear_recurrence": [P, I, P, I, P, I, P, I, P, P, F, F, P, L, P, I, P, P, I, I, I, I,
-                                  I, I, I, I, P],
+        "llm_linear_recurrence": [P, I, P, I, P, I, P, I, P, I, P, P, F, F, P, L, P, I, P, P, I, I,
+                                  I, I, I, I, I, I, P],
+        "llm_log_gate_scan": [P, P, I, P, P, F, P, L, P, I, P, P, I, I, I, I, P],
+        "llm_memory_out_norm": [P, I, P, I, P, I, P, P, I, I, I, I, I, F, F, P],
+        "llm_stream_step": [P, L, I, P, P, P, I, I, P, P, F, P, I, P, I, I, P],
+        "llm_stream_fill": [P, L, I, I, I, P],
+        "llm_gated_act": [P, P, P, I, I, I, I, P],
+        "llm_scale_soft_cap": [P, L, F, F, P],
+        "llm_latent_store": [P, I, P, P, P, I, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P],
+        "llm_latent_query": [P, I, P, I, P, P, I, I, I, I, I, I, P],
+        "llm_gemm_simt_batched": [P, P, P, I, I, I, I, I, I, I, I, I, L, L, L, P],
+        "llm_moe_route": [P, I, I, I, I, P, P, P],
+        "llm_moe_gate_up_rows": [P, P, P, P, I, I, I, I, I, P],
+        "llm_moe_down_rows": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, P],
         "llm_causal_conv_silu": [P, I, P, P, P, L, P, P, I, I, I, P, I, I, I, P],
         "llm_gated_group_norm": [P, I, P, I, P, I, P, I, P, I, P, I, I, I, I, I, F, I, P],
     }
@@ -293,14 +305,16 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       v_cache: torch.Tensor, page_stride: int, block_table: torch.Tensor,
                       row_slot: torch.Tensor, row_pos: torch.Tensor, num_heads: int,
                       num_kv_heads: int, head_dim: int, page_size: int, scale: float,
-                      window: Optional[int]) -> None:
-    _cuda(q, out, k_cache, v_cache, block_table, row_slot, row_pos)
+                      window: Optional[int], sink: Optional[torch.Tensor] = None,
+                      value_dim: int = 0) -> None:
+    _cuda(q, out, k_cache, v_cache, block_table, row_slot, row_pos, sink)
     assert q.dtype == out.dtype == k_cache.dtype and q.is_contiguous() and out.is_contiguous()
     rows = q.shape[0]
     _check(lib().llm_attention_generic(
         _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _dt(q), page_stride, _ptr(block_table),
         block_table.stride(0), _ptr(row_slot), _ptr(row_pos), rows, num_heads, num_kv_heads,
-        head_dim, page_size, float(scale), int(window or 0), _stream()),
+        head_dim, page_size, float(scale), int(window or 0), _ptr(sink), int(value_dim),
+        _stream()),
         f"attention (head_dim {head_dim})")
 
 
@@ -398,7 +412,7 @@ def segment_table(row_slot: torch.Tensor, seg: torch.Tensor) -> None:
                                    _stream()), "segment_table")
 
 
-DECAY_VECTOR, DECAY_SIGMOID_POW, DECAY_RATE_STEP = 0, 1, 2
+DECAY_VECTOR, DECAY_SIGMOID_POW, DECAY_RATE_STEP, DECAY_SCALAR_INPUT = 0, 1, 2, 3
 
 
 def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch.Tensor,
@@ -406,7 +420,8 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torc
                       seg: Optional[torch.Tensor], heads: int, groups: int, key_dim: int,
                       value_dim: int, kind: int, q_scale: float = 1.0, exponent: float = 1.0,
                       rate_log: Optional[torch.Tensor] = None,
-                      step_bias: Optional[torch.Tensor] = None, n_requests: int = 0) -> None:
+                      step_bias: Optional[torch.Tensor] = None, n_requests: int = 0,
+                      input_weight: Optional[torch.Tensor] = None, ones: bool = False) -> None:
     """Per request and head ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_scale q_t)`` over
     the rows of the step in order.  q, k float32 [rows, groups * key_dim], v and out float32
     [rows, heads * value_dim] (column slices of wider matrices are fine); head h uses group
@@ -415,17 +430,23 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torc
     comes from ``d``: DECAY_VECTOR ``a = d`` and DECAY_SIGMOID_POW ``a = sigmoid(d)^exponent``
     with d [rows, heads * key_dim]; DECAY_RATE_STEP with d [rows, heads]:
     ``step = softplus(d + step_bias[h])``, ``a = exp(-exp(rate_log[h]) step)`` and v is
-    multiplied by step.  ``seg``: the table of :func:`segment_table` with ``n_requests`` the
+    multiplied by step; DECAY_SCALAR_INPUT with d and ``input_weight`` [rows, heads] (equal row
+    strides): ``a = d`` and v is multiplied by the input weight.  ``ones``: v has
+    ``value_dim - 1`` channels per head and the last state column is fed the constant 1 (it then
+    holds the decayed sum of the keys, and the last output channel its product with q).
+    ``seg``: the table of :func:`segment_table` with ``n_requests`` the
     number of requests that have rows in the step, or None when every row is a request of its
     own."""
-    _cuda(q, k, v, d, state, out, row_slot, seg, rate_log, step_bias)
+    _cuda(q, k, v, d, state, out, row_slot, seg, rate_log, step_bias, input_weight)
     for t in (q, k, v, d, state, out):
         assert t.dtype == torch.float32 and t.stride(-1) == 1
     rows = out.shape[0]
     assert state.dim() == 2 and state.shape[1] >= heads * value_dim * key_dim
+    if input_weight is not None:
+        assert input_weight.dtype == torch.float32 and input_weight.stride(0) == d.stride(0)
     _check(lib().llm_linear_recurrence(
         _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(d), d.stride(0),
-        _ptr(rate_log), _ptr(step_bias), float(exponent), float(q_scale), _ptr(state),
+        _ptr(input_weight), int(ones), _ptr(rate_log), _ptr(step_bias), float(exponent), float(q_scale), _ptr(state),
         state.stride(0), _ptr(out), out.stride(0), _ptr(seg), _ptr(row_slot), rows,
         int(n_requests), int(seg is None), heads, groups, key_dim, value_dim, kind, _stream()),
         f"linear_recurrence (key_dim {key_dim})")
@@ -710,7 +731,7 @@ def gate_up_silu(ctx, h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tenso
 
 
 FLASH_HEAD_DIMS = (32, 64, 128)
-ATTENTION_MAX_HEAD_DIM = 256      # MAX_HD of attention_generic.cu, the kernel of last resort
+ATTENTION_MAX_HEAD_DIM = 640      # MAX_HD of attention_generic.cu, the kernel of last resort
 
 
 def attention_refusal(num_heads: int, num_kv_heads: int, head_dim: int) -> Optional[str]:
@@ -956,3 +977,212 @@ def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int =
 DECODE_TMA_TILE = 32      # keys of a tile of attention_decode_tma.cu
 DECODE_TMA_CTAS_PER_SM = 4    # its one-warp CTAs that fit an SM at head size 128
 PERSISTENT_ATTENTION_MAX_KEYS = 6144
+
+
+# ---------------------------------------------------------------------------------------------
+# parts that other designs than the first two brought: several residual streams, a matrix memory
+# with exponential gates, attention through latents, routed experts, other activations
+
+def log_gate_scan(zi: torch.Tensor, zf: torch.Tensor, bias_i: Optional[torch.Tensor],
+                  bias_f: Optional[torch.Tensor], cap: float, m_state: torch.Tensor,
+                  out: torch.Tensor, row_slot: torch.Tensor, seg: Optional[torch.Tensor],
+                  heads: int, n_requests: int = 0) -> None:
+    """The exponential gates of a matrix memory per (row, head), kept in range by a running
+    maximum ``m`` that is carried per request in ``m_state`` ([slots, >= heads] float32 view):
+    ``i = cap tanh((zi + bias_i) / cap)``, ``f = log sigmoid(cap tanh((zf + bias_f) / cap))``
+    (``cap`` 0: no cap), ``m_t = max(f_t + m_(t-1), i_t)``; ``out[row]`` = [exp(f + m_(t-1) -
+    m_t) | exp(i - m_t) | m_t], each ``heads`` wide.  zi, zf: float32 [rows, heads] with equal
+    row strides."""
+    _cuda(zi, zf, bias_i, bias_f, m_state, out, row_slot, seg)
+    rows = zi.shape[0]
+    assert zi.dtype == zf.dtype == out.dtype == m_state.dtype == torch.float32
+    assert zi.stride(0) == zf.stride(0) and zi.stride(1) == 1 and zf.stride(1) == 1
+    assert out.shape == (rows, 3 * heads) and out.stride(1) == 1 and m_state.stride(1) == 1
+    _check(lib().llm_log_gate_scan(_ptr(zi), _ptr(zf), zi.stride(0), _ptr(bias_i), _ptr(bias_f),
+                                   float(cap), _ptr(m_state), m_state.stride(0), _ptr(out),
+                                   out.stride(0), _ptr(seg), _ptr(row_slot), rows, int(n_requests),
+                                   int(seg is None), heads, _stream()), "log_gate_scan")
+
+
+def memory_out_norm(o: torch.Tensor, m: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor,
+                    out: torch.Tensor, heads: int, value_dim: int, eps: float,
+                    floor: float) -> None:
+    """``y = o[..., :V] / (max(|o[..., V]|, exp(-m)) + floor)`` per (row, head), then
+    ``out = y / rms(y) * weight * sigmoid(gate)``.  o: float32 [rows, heads * (V + 1)]; m: float32
+    [rows, heads] (a column slice is fine); gate: float32 [rows, heads * V] (a column slice is
+    fine); weight: float32 [heads * V]; out: [rows, heads * V] in the activation type."""
+    _cuda(o, m, gate, weight, out)
+    rows = out.shape[0]
+    assert o.dtype == m.dtype == gate.dtype == weight.dtype == torch.float32
+    assert o.shape == (rows, heads * (value_dim + 1)) and o.stride(1) == 1 and m.stride(1) == 1
+    assert gate.stride(1) == 1 and out.stride(1) == 1 and weight.numel() == heads * value_dim
+    _check(lib().llm_memory_out_norm(_ptr(o), o.stride(0), _ptr(m), m.stride(0), _ptr(gate),
+                                     gate.stride(0), _ptr(weight), _ptr(out), _dt(out),
+                                     out.stride(0), rows, heads, value_dim, float(eps),
+                                     float(floor), _stream()), "memory_out_norm")
+
+
+STREAM_KEEP_WIDTH = 4096     # widest row of a stream step that does not store its new streams
+
+
+def stream_step(xs: torch.Tensor, y: Optional[torch.Tensor] = None,
+                mix: Optional[torch.Tensor] = None, out_coef: Optional[torch.Tensor] = None,
+                clear_y: bool = False, store: bool = True,
+                in_coef: Optional[torch.Tensor] = None, weight: Optional[torch.Tensor] = None,
+                eps: float = 0.0, out: Optional[torch.Tensor] = None,
+                rows_index: Optional[torch.Tensor] = None) -> None:
+    """One sublayer boundary of a model with several residual streams ``xs`` (float32
+    [S, rows, width]).  With ``y`` (float32 [rows, width]): ``xs[t] <- sum_s mix[s, t] xs[s] +
+    out_coef[t] y`` for all t at once (``clear_y`` zeroes what was read of y).  With ``in_coef``:
+    ``out = rms_norm(sum_s in_coef[s] xs[s]) * weight`` from the new streams.  ``rows_index``: the
+    rows to work on (``out`` has one row per index), else all rows."""
+    _cuda(xs, y, mix, out_coef, in_coef, weight, out, rows_index)
+    S, rows, width = xs.shape
+    assert xs.dtype == torch.float32 and xs.is_contiguous()
+    if y is not None:
+        assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (rows, width)
+        assert mix.dtype == out_coef.dtype == torch.float32 and mix.is_contiguous()
+        assert mix.numel() == S * S and out_coef.numel() == S
+    n = rows
+    if in_coef is not None:
+        assert in_coef.dtype == weight.dtype == torch.float32 and in_coef.numel() == S
+        assert weight.numel() == width and out.is_contiguous() and out.shape[1] == width
+        n = out.shape[0]
+    if rows_index is not None:
+        assert rows_index.dtype == torch.int32 and rows_index.numel() == n
+    _check(lib().llm_stream_step(_ptr(xs), xs.stride(0), S, _ptr(y), _ptr(mix), _ptr(out_coef),
+                                 int(clear_y), int(store), _ptr(in_coef), _ptr(weight),
+                                 float(eps), _ptr(out), _dt(out) if out is not None else F32,
+                                 _ptr(rows_index), n, width, _stream()), "stream_step")
+
+
+def stream_fill(xs: torch.Tensor) -> None:
+    """xs[s] = xs[0] for every other stream s."""
+    _cuda(xs)
+    S, rows, width = xs.shape
+    assert xs.dtype == torch.float32 and xs.is_contiguous()
+    _check(lib().llm_stream_fill(_ptr(xs), xs.stride(0), S, rows, width, _stream()),
+           "stream_fill")
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+              activation: str) -> None:
+    """out[t][j] = act(gate_up[t][j] + bias[j]) * (gate_up[t][ff + j] + bias[ff + j])."""
+    _cuda(gate_up, bias, out)
+    rows, ff = out.shape
+    assert gate_up.dtype == torch.float32 and gate_up.is_contiguous() and out.is_contiguous()
+    assert gate_up.shape == (rows, 2 * ff)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * ff)
+    _check(lib().llm_gated_act(_ptr(gate_up), _ptr(bias), _ptr(out), _dt(out), rows, ff,
+                               ACTIVATIONS[activation], _stream()), "gated_act")
+
+
+def scale_soft_cap(z: torch.Tensor, scale: float, cap: float) -> None:
+    """z <- cap tanh(z scale / cap) in place (``cap`` 0: z <- z scale); float32, contiguous."""
+    _cuda(z)
+    assert z.dtype == torch.float32 and z.is_contiguous()
+    _check(lib().llm_scale_soft_cap(_ptr(z), z.numel(), float(scale), float(cap), _stream()),
+           "scale_soft_cap")
+
+
+def latent_store(proj: torch.Tensor, q_weight: torch.Tensor, c_weight: torch.Tensor,
+                 cos_sin: Optional[torch.Tensor], cq_out: torch.Tensor, view,
+                 row_slot: torch.Tensor, row_pos: torch.Tensor, q_rank: int, kv_rank: int,
+                 rot_dim: int, eps: float, write_cache: bool = True) -> None:
+    """From proj (float32 [rows, >= q_rank + kv_rank + rot_dim]): the normed query latent into
+    ``cq_out`` and the key row [normed latent | rotated key part] into the paged cache ``view``
+    (K plane whole, V plane the latent alone).  ``cos_sin``: float32 [rows, pairs, 2]."""
+    _cuda(proj, q_weight, c_weight, cos_sin, cq_out, view.k, view.v, row_slot, row_pos)
+    rows = cq_out.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and cq_out.is_contiguous()
+    assert cq_out.dtype == view.k.dtype and cq_out.shape[1] == q_rank
+    half = 0 if cos_sin is None else cos_sin.shape[1]
+    _check(lib().llm_latent_store(_ptr(proj), proj.stride(0), _ptr(q_weight), _ptr(c_weight),
+                                  _ptr(cos_sin), half, _ptr(cq_out), _ptr(view.k), _ptr(view.v),
+                                  _dt(cq_out), view.page_stride, _ptr(view.block_table),
+                                  view.block_table.stride(0), _ptr(row_slot), _ptr(row_pos), rows,
+                                  view.page_size, q_rank, kv_rank, rot_dim, float(eps),
+                                  int(write_cache), _stream()), "latent_store")
+
+
+def latent_query(q: torch.Tensor, cos_sin: Optional[torch.Tensor], q_plain: torch.Tensor,
+                 q_full: torch.Tensor, heads: int, dim: int, rot_dim: int, kv_rank: int) -> None:
+    """From q (float32 [rows, heads * (dim + rot_dim)]): every head's plain part rounded into
+    ``q_plain`` [rows, heads * dim], its rotated part into ``q_full`` [rows, heads * (kv_rank +
+    rot_dim)] behind the first kv_rank channels."""
+    _cuda(q, cos_sin, q_plain, q_full)
+    rows = q.shape[0]
+    assert q.dtype == torch.float32 and q.stride(1) == 1
+    assert q_plain.is_contiguous() and q_full.is_contiguous() and q_plain.dtype == q_full.dtype
+    half = 0 if cos_sin is None else cos_sin.shape[1]
+    _check(lib().llm_latent_query(_ptr(q), q.stride(0), _ptr(cos_sin), half, _ptr(q_plain),
+                                  _ptr(q_full), _dt(q_full), rows, heads, dim, rot_dim, kv_rank,
+                                  _stream()), "latent_query")
+
+
+def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """A map per head: ``out[r, h, :] = w[h] @ a[r, h, :]``.  a [rows, H, in] and out
+    [rows, H, out_features] may be views with a row stride and a head stride (the last dimension dense); w
+    [H, out_features, in] contiguous.  bfloat16 operands whose rows are whole 16-byte units go to
+    the tensor-core product head by head, everything else to one batched CUDA-core launch."""
+    _cuda(a, w, out)
+    rows, H, k = a.shape
+    n = w.shape[1]
+    assert w.shape == (H, n, k) and w.is_contiguous() and out.shape == (rows, H, n)
+    assert a.stride(2) == 1 and out.stride(2) == 1 and a.dtype == w.dtype
+    if all(_tc_ok(a[:, h], w[h], out[:, h]) for h in range(H)):
+        for h in range(H):
+            gemm_tcgen05(a[:, h], w[h], out[:, h], 0)
+        return
+    _check(lib().llm_gemm_simt_batched(_ptr(a), _ptr(w), _ptr(out), _dt(a), _dt(out), rows, n, k,
+                                       a.stride(0), k, out.stride(0), H, a.stride(1), n * k,
+                                       out.stride(1), _stream()), "head_linear")
+
+
+def moe_route(z: torch.Tensor, experts: int, top: int, ids: torch.Tensor, wts: torch.Tensor
+              ) -> None:
+    """Per row the ``top`` largest of the first ``experts`` logits of z (float32, a column slice
+    is fine) into ``ids`` (int32 [rows, top]) and the softmax over the chosen into ``wts``."""
+    _cuda(z, ids, wts)
+    rows = z.shape[0]
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and z.shape[1] >= experts
+    assert ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (rows, top)
+    assert wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == (rows, top)
+    _check(lib().llm_moe_route(_ptr(z), z.stride(0), rows, experts, top, _ptr(ids), _ptr(wts),
+                               _stream()), "moe_route")
+
+
+def moe_gate_up_rows(h: torch.Tensor, gate_up: torch.Tensor, ids: torch.Tensor,
+                     act: torch.Tensor) -> None:
+    """act[r, k] = silu(Wg_e h_r) * (Wu_e h_r), e = ids[r, k]; gate_up [E, 2 ff, width]."""
+    _cuda(h, gate_up, ids, act)
+    rows, width = h.shape
+    top = ids.shape[1]
+    ff = gate_up.shape[1] // 2
+    assert h.is_contiguous() and gate_up.is_contiguous() and act.is_contiguous()
+    assert h.dtype == gate_up.dtype == act.dtype and act.shape == (rows, top, ff)
+    _check(lib().llm_moe_gate_up_rows(_ptr(h), _ptr(gate_up), _ptr(ids), _ptr(act), _dt(h), rows,
+                                      width, ff, top, _stream()), "moe_gate_up_rows")
+
+
+def moe_down_rows(act: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
+                  y: torch.Tensor, accumulate: bool, shared: Optional[torch.Tensor] = None,
+                  shared_gate: Optional[torch.Tensor] = None) -> None:
+    """y[r] (+)= sum_k wts[r, k] Wd_e act[r, k] (+ sigmoid(shared_gate[r]) shared[r]);
+    down [E, width, ff]; y, shared float32 [rows, width]; shared_gate float32 [rows] (strided)."""
+    _cuda(act, down, ids, wts, y, shared, shared_gate)
+    rows, top, ff = act.shape
+    width = down.shape[1]
+    assert act.is_contiguous() and down.is_contiguous() and act.dtype == down.dtype
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (rows, width)
+    if shared is not None:
+        assert shared.dtype == torch.float32 and shared.is_contiguous()
+        assert shared_gate.dtype == torch.float32 and shared_gate.shape[0] == rows
+    _check(lib().llm_moe_down_rows(_ptr(act), _ptr(down), _ptr(ids), _ptr(wts), _ptr(shared),
+                                   _ptr(shared_gate),
+                                   shared_gate.stride(0) if shared_gate is not None else 0,
+                                   _ptr(y), _dt(act), rows, width, ff, top, int(accumulate),
+                                   _stream()), "moe_down_rows")

@@ -18,10 +18,14 @@ class PreNormResidualBlock:
     def __init__(self, spec: PartSpec, layer: LayerSpec, weights: Dict[str, torch.Tensor],
                  dtype, device):
         self.mixer_norm = build_part("norm", spec["mixer_norm"], weights, dtype, device)
-        self.ffn_norm = build_part("norm", spec["feed_forward_norm"], weights, dtype, device)
+        # (a layer whose feed-forward is of kind ``none`` has only the first sublayer)
+        self.ffn_norm = None if spec.get("feed_forward_norm") is None else \
+            build_part("norm", spec["feed_forward_norm"], weights, dtype, device)
         self.mixer = build_part("mixer", layer.mixer, weights, dtype, device)
         self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, dtype,
                                        device)
+        if self.ffn_norm is None and layer.feed_forward.kind != "none":
+            raise ConfigError("a pre-norm block with a feed-forward needs its norm")
 
     def cache_needs(self):
         """What this block keeps between steps: one need per stateful part, in a fixed order
@@ -35,14 +39,15 @@ class PreNormResidualBlock:
     @property
     def graph_safe(self) -> bool:
         return all(graph_safe(p) for p in (self.mixer_norm, self.ffn_norm, self.mixer,
-                                           self.feed_forward))
+                                           self.feed_forward) if p is not None)
 
     def forward(self, ctx: StepContext, call: BoundCall, x: torch.Tensor) -> None:
         h = ctx.buffer("block.h", x.shape)
         self.mixer_norm.apply(ctx, x, h)
         self.mixer.forward(ctx, call.for_need(0) if call.cache_entries else call, h, x)
-        self.ffn_norm.apply(ctx, x, h)
-        self.feed_forward.forward(ctx, h, x)
+        if self.ffn_norm is not None:
+            self.ffn_norm.apply(ctx, x, h)
+            self.feed_forward.forward(ctx, h, x)
 
 
 class OutputNormResidualBlock:
@@ -120,5 +125,81 @@ class OutputNormResidualBlock:
         ctx.shared["block.h behind"] = (x.data_ptr(), call.index)
 
 
+class HyperConnectionBlock:
+    """Pre-norm sublayers over S residual streams ``xs`` [S, rows, hidden] (32-bit).  Sublayer q
+    reads ``u = sum_s in_q[s] xs[s]``, computes ``y = sublayer(norm_q(u))`` and writes, for all
+    streams at once from the old ones, ``xs[t] <- sum_s mix_q[s, t] xs[s] + out_q[t] y``.  One
+    kernel does a sublayer's write together with the next sublayer's read and norm; the write of
+    a layer's last sublayer is left to the block that runs next (or to the end of the step),
+    which finds it under ``ctx.shared["streams.pending"]``.  Tensor roles: ``mixer_in`` [S],
+    ``mixer_out`` [S], ``mixer_mix`` [S, S] (indexed [from, to]) and the same for
+    ``feed_forward_*``; a feed-forward of kind ``none`` leaves a layer with one sublayer."""
+
+    def __init__(self, spec: PartSpec, layer: LayerSpec, weights: Dict[str, torch.Tensor],
+                 dtype, device):
+        self.streams = int(spec["streams"])
+
+        def coef(role, shape):
+            t = optional_tensor_of(spec, role, weights)
+            if t is None or tuple(t.shape) != shape:
+                raise ConfigError(f"hyper-connection block: tensor '{role}' of shape {shape}")
+            return t.to(device=device, dtype=torch.float32).contiguous()
+
+        S = self.streams
+        self.mixer_norm = build_part("norm", spec["mixer_norm"], weights, dtype, device)
+        self.mixer = build_part("mixer", layer.mixer, weights, dtype, device)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, dtype,
+                                       device)
+        self.has_feed_forward = layer.feed_forward.kind != "none"
+        self.mixer_coef = (coef("mixer_in", (S,)), coef("mixer_out", (S,)),
+                           coef("mixer_mix", (S, S)))
+        self.ffn_norm = self.ffn_coef = None
+        if self.has_feed_forward:
+            self.ffn_norm = build_part("norm", spec["feed_forward_norm"], weights, dtype, device)
+            self.ffn_coef = (coef("feed_forward_in", (S,)), coef("feed_forward_out", (S,)),
+                             coef("feed_forward_mix", (S, S)))
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and type(norm) is not RmsNorm:
+                raise ConfigError("the hyper-connection block fuses an RMS norm with the mixing "
+                                  f"of the streams; it has no form for {type(norm).__name__}")
+
+    def cache_needs(self):
+        return [self.mixer.cache_need()]
+
+    def streamed_weights(self):
+        return streamed_weights_of(self.mixer) + streamed_weights_of(self.feed_forward)
+
+    @property
+    def graph_safe(self) -> bool:
+        return graph_safe(self.mixer) and graph_safe(self.feed_forward)
+
+    def forward(self, ctx: StepContext, call: BoundCall, xs: torch.Tensor) -> None:
+        if xs.dim() != 3 or xs.shape[0] != self.streams:
+            raise RuntimeError(f"a hyper-connection block of {self.streams} streams was given a "
+                               f"residual of shape {tuple(xs.shape)}")
+        shape = tuple(xs.shape[1:])
+        # the sublayers' last products add partial sums when a step has few rows: their
+        # destination is then kept at zero (the stream kernel clears what it has read)
+        kept_zero = ctx.rows <= kernels.SPLIT_K_MAX_ROWS
+        y = ctx.buffer("block.y.z" if kept_zero else "block.y", shape, torch.float32,
+                       zero=kept_zero)
+        h = ctx.buffer("block.h", shape)
+        write = ctx.shared.pop("streams.pending", None) or {}
+        cin, cout, mix = self.mixer_coef
+        kernels.stream_step(xs, in_coef=cin, weight=self.mixer_norm.weight,
+                            eps=self.mixer_norm.eps, out=h, **write)
+        self.mixer.forward(ctx, call.for_need(0) if call.cache_entries else call, h, y,
+                           accumulate=kept_zero)
+        write = dict(y=y, mix=mix, out_coef=cout, clear_y=kept_zero)
+        if self.has_feed_forward:
+            cin, cout, mix = self.ffn_coef
+            kernels.stream_step(xs, in_coef=cin, weight=self.ffn_norm.weight,
+                                eps=self.ffn_norm.eps, out=h, **write)
+            self.feed_forward.forward(ctx, h, y, accumulate=kept_zero)
+            write = dict(y=y, mix=mix, out_coef=cout, clear_y=kept_zero)
+        ctx.shared["streams.pending"] = write
+
+
 register_part("block", "pre_norm_residual", PreNormResidualBlock, replace=True)
+register_part("block", "hyper_connection", HyperConnectionBlock, replace=True)
 register_part("block", "output_norm_residual", OutputNormResidualBlock, replace=True)

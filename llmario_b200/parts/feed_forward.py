@@ -1,6 +1,12 @@
 """Gated feed-forward: ``y = W_down (silu(W_gate h) * (W_up h))`` with
 ``silu(z) = z / (1 + exp(-z))``, no biases (crates/engine/model/src/forward.rs:500-530;
-crates/engine/cpu/src/ops.rs:83-99).  Gate and up are one product over stacked rows."""
+crates/engine/cpu/src/ops.rs:83-99).  Gate and up are one product over stacked rows.
+
+Beside it: the same form with a choice of activation and optional biases (kind ``gated``), and
+routed experts (kind ``moe``): a router's logits (32-bit) choose ``top`` of ``experts`` small
+silu-gated feed-forwards per token, whose outputs are summed with the softmax over the chosen
+logits as weights; an optional shared feed-forward runs for every token and is added multiplied
+by the sigmoid of one more projection of the input (one number per token)."""
 from __future__ import annotations
 
 from typing import Dict
@@ -8,8 +14,8 @@ from typing import Dict
 import torch
 
 from .. import kernels
-from ..config.spec import PartSpec
-from .base import StepContext, register_part, tensor_of
+from ..config.spec import ConfigError, PartSpec
+from .base import StepContext, build_part, optional_tensor_of, register_part, tensor_of
 from .linear import Linear
 
 
@@ -61,5 +67,108 @@ class NoFeedForward:
             raise RuntimeError("a layer without a feed-forward has no result to hand over")
 
 
+class GatedFeedForward:
+    """``y = W_down (act(W_gate h + b_gate) * (W_up h + b_up)) + b_down`` with ``activation``
+    ``silu`` or ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))); the biases
+    (tensor roles ``gate_bias``, ``up_bias``, ``down_bias``) are optional.  Without biases and
+    with silu it is the standard part and runs on its fused product."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = int(spec["hidden_size"])
+        self.ff = int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "silu")
+        if self.activation not in kernels.ACTIVATIONS:
+            raise ConfigError(f"gated feed-forward: activation '{self.activation}' (known: "
+                              f"{', '.join(kernels.ACTIVATIONS)})")
+        b = {r: optional_tensor_of(spec, r + "_bias", weights) for r in ("gate", "up", "down")}
+        if (b["gate"] is None) != (b["up"] is None):
+            raise ConfigError("gated feed-forward: the gate's and the up projection's biases "
+                              "come together")
+        self.plain = None
+        if self.activation == "silu" and all(v is None for v in b.values()):
+            self.plain = SwiGLU(spec, weights, dtype, device)
+            return
+        self.gate_up = Linear.stacked([tensor_of(spec, "gate", weights),
+                                       tensor_of(spec, "up", weights)])
+        self.gate_up_bias = None if b["gate"] is None else torch.cat(
+            [b["gate"].to(torch.float32), b["up"].to(torch.float32)]).contiguous()
+        self.down = Linear(tensor_of(spec, "down", weights), b["down"])
+
+    def streamed_weights(self):
+        if self.plain is not None:
+            return self.plain.streamed_weights()
+        return [self.gate_up.weight, self.down.weight]
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        if self.plain is not None:
+            self.plain.forward(ctx, h, x, accumulate=accumulate)
+            return
+        rows = ctx.rows
+        gu = ctx.buffer("ffn.gate_up", (rows, 2 * self.ff), torch.float32)
+        self.gate_up(h, gu)
+        act = ctx.buffer("ffn.act", (rows, self.ff))
+        kernels.gated_act(gu, self.gate_up_bias, act, self.activation)
+        self.down(act, x, accumulate=accumulate)
+
+
+class RoutedExperts:
+    graph_safe = True      # which experts a row uses is read on the device
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = W = int(spec["hidden_size"])
+        self.ff = ff = int(spec["intermediate_size"])
+        self.experts = E = int(spec["experts"])
+        self.top = int(spec["top"])
+        if not 1 <= self.top <= min(E, 16):
+            raise ConfigError(f"routed experts: top {self.top} of {E} (at most 16)")
+        router = tensor_of(spec, "router", weights).to(torch.float32)
+        bias = optional_tensor_of(spec, "router_bias", weights)
+        bias = torch.zeros(E, device=router.device) if bias is None else bias.to(torch.float32)
+        sg = optional_tensor_of(spec, "shared_gate", weights)
+        self.shared = None
+        if spec.get("shared") is not None:
+            if sg is None or tuple(sg.shape) != (1, W):
+                raise ConfigError("routed experts: a shared expert needs its gate [1, hidden]")
+            self.shared = build_part("feed_forward", spec["shared"], weights, dtype, device)
+            router = torch.cat([router, sg.to(torch.float32)])
+            bias = torch.cat([bias, torch.zeros(1, device=bias.device)])
+        # the router (and the shared expert's gate as its last row) stays 32-bit
+        self.router = Linear(router.contiguous(), bias)
+        self.gate_up = torch.stack([torch.cat([tensor_of(spec, f"gate{e}", weights),
+                                               tensor_of(spec, f"up{e}", weights)])
+                                    for e in range(E)]).contiguous()           # [E, 2 ff, W]
+        self.down = torch.stack([tensor_of(spec, f"down{e}", weights)
+                                 for e in range(E)]).contiguous()              # [E, W, ff]
+        if tuple(self.gate_up.shape) != (E, 2 * ff, W) or tuple(self.down.shape) != (E, W, ff):
+            raise ConfigError("routed experts: the experts' matrices do not have the spec's sizes")
+
+    def streamed_weights(self):
+        """(What a step reads of the experts depends on its tokens: all of them are counted.)"""
+        shared = self.shared.streamed_weights() if self.shared is not None else []
+        return [self.router.weight, self.gate_up, self.down] + shared
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        rows, E, top = ctx.rows, self.experts, self.top
+        z = ctx.buffer("moe.logits", (rows, self.router.out_features), torch.float32)
+        self.router(h, z)
+        ids = ctx.buffer("moe.ids", (rows, top), torch.int32)
+        wts = ctx.buffer("moe.weights", (rows, top), torch.float32)
+        kernels.moe_route(z, E, top, ids, wts)
+        act = ctx.buffer("moe.act", (rows, top, self.ff))
+        kernels.moe_gate_up_rows(h, self.gate_up, ids, act)
+        shared = gate = None
+        if self.shared is not None:
+            shared = ctx.buffer("moe.shared", (rows, self.hidden), torch.float32)
+            self.shared.forward(ctx, h, shared, accumulate=False)
+            gate = z[:, E]
+        kernels.moe_down_rows(act, self.down, ids, wts, x, accumulate, shared, gate)
+
+
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+register_part("feed_forward", "gated", GatedFeedForward, replace=True)
+register_part("feed_forward", "moe", RoutedExperts, replace=True)
 register_part("feed_forward", "none", NoFeedForward, replace=True)

@@ -1,6 +1,7 @@
 """Token embedding (row gather, no scaling: crates/engine/model/src/forward.rs:343-349) and the
 output head (``logits = H h`` with ``H`` the output matrix or, when tied, the embedding table:
-forward.rs:303-316)."""
+forward.rs:303-316).  Options of the head: ``scale`` multiplies the logits, ``soft_cap`` then
+bounds them smoothly (``cap * tanh(z / cap)``)."""
 from __future__ import annotations
 
 from typing import Dict
@@ -33,12 +34,16 @@ class LinearHead:
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
         self.proj = Linear(tensor_of(spec, "weight", weights))
         self.vocab = self.proj.out_features
+        self.scale = float(spec.get("scale") or 1.0)
+        self.soft_cap = float(spec.get("soft_cap") or 0.0)
 
     def streamed_weights(self):
         return [self.proj.weight]
 
     def forward(self, ctx: StepContext, h: torch.Tensor, logits: torch.Tensor) -> None:
         self.proj(h, logits)
+        if self.scale != 1.0 or self.soft_cap:
+            kernels.scale_soft_cap(logits, self.scale, self.soft_cap)
 
 
 register_part("embedding", "token_embedding", TokenEmbedding, replace=True)

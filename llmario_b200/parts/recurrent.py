@@ -11,7 +11,16 @@
   silu first, B and C are shared by the heads of a group; ``y silu(z)`` is RMS-normed in equal
   groups of channels and projected.
 
-Both are the same recurrence (``csrc/recurrent.cu``), told by data how the decay is made.  The
+* ``mlstm``: a matrix memory with exponential input and forget gates per head, kept in range by
+  a running maximum ``m_t = max(f_t + m_(t-1), i_t)`` (m starts at 0):
+  ``S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) + e^(i_t - m_t) k_t v_t^T``, a normaliser ``z_t`` that is
+  the same sum with ``k_t`` alone, ``o_t = S_t^T q_t / (max(|z_t . q_t|, e^(-m_t)) + floor)``
+  with ``q`` scaled by ``key_dim^(-1/2)``, ``i = cap tanh((W_i h + b_i) / cap)`` and
+  ``f = log sigmoid(cap tanh((W_f h + b_f) / cap))``; each head's output is divided by its root
+  mean square, multiplied by a gain per channel and by ``sigmoid(W_g h)``, and projected.
+
+All are the same recurrence (``csrc/recurrent.cu``), told by data how the decay is made (the
+matrix memory's normaliser is one more state column that is fed ones).  The
 state (and the convolution's last inputs) is 32-bit and lives in the request's fixed-size state
 slot of the cache manager, which clears a slot when a request is opened in it.  Everything
 behind the projections is computed in 32-bit.  Which rows belong to which request is read on
@@ -192,5 +201,68 @@ class StateSpaceMixer:
         self.o_proj(gated, x, accumulate=accumulate)
 
 
+class MatrixMemory:
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = int(spec["hidden_size"])
+        self.heads = int(spec["num_heads"])
+        self.key_dim = int(spec["key_dim"])
+        self.value_dim = int(spec["value_dim"])
+        self.gate_cap = float(spec.get("gate_cap") or 0.0)      # 0: the gates are not capped
+        self.eps = float(spec["eps"])
+        self.floor = float(spec.get("floor", 1e-6))
+        if self.key_dim > 512:
+            raise ConfigError(f"mlstm: key_dim {self.key_dim}: the recurrence keeps at most 512 "
+                              "key channels of a state column in registers")
+        H, K, V = self.heads, self.key_dim, self.value_dim
+        t = {r: tensor_of(spec, r, weights) for r in ("q", "k", "v", "g", "i", "f", "o")}
+        self.col_k, self.col_v, self.col_g = H * K, 2 * H * K, 2 * H * K + H * V
+        self.col_i, self.col_f = 2 * H * K + 2 * H * V, 2 * H * K + 2 * H * V + H
+        self.in_proj = _padded_rows([t[r] for r in ("q", "k", "v", "g", "i", "f")], self.hidden)
+        self.o_proj = Linear(t["o"])
+        bi, bf = (optional_tensor_of(spec, r, weights) for r in ("i_bias", "f_bias"))
+        self.bias_i = None if bi is None else _f32(bi, device)
+        self.bias_f = None if bf is None else _f32(bf, device)
+        self.norm_weight = _f32(tensor_of(spec, "norm", weights), device)
+        if self.norm_weight.numel() != H * V:
+            raise ConfigError("mlstm: the output norm has one weight per value channel of every head")
+        self.state_floats = H * (V + 1) * K       # per head V value columns and the normaliser's
+
+    def cache_need(self):
+        """Every head's matrix with the normaliser as one more column, then every head's running
+        maximum of the gates."""
+        return FixedState((self.state_floats + self.heads,), torch.float32)
+
+    def streamed_weights(self):
+        return [self.in_proj.weight, self.o_proj.weight]
+
+    def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        rows, H, K, V = ctx.rows, self.heads, self.key_dim, self.value_dim
+        state = ctx.cache.state_of(call.cache_entry)
+        if state is None:
+            raise RuntimeError(f"run-order entry {call.index}: the recurrence needs a state slot")
+        seg = step_segments(ctx)
+        proj = ctx.buffer("mlstm.proj", (rows, self.in_proj.out_features), torch.float32)
+        self.in_proj(h, proj)                    # [q | k | v | g | i | f]
+        gates = ctx.buffer("mlstm.gates", (rows, 3 * H), torch.float32)    # [keep | take | m]
+        kernels.log_gate_scan(proj[:, self.col_i:self.col_i + H], proj[:, self.col_f:self.col_f + H],
+                              self.bias_i, self.bias_f, self.gate_cap,
+                              state[:, self.state_floats:], gates, ctx.row_slot, seg, H,
+                              n_requests=len(ctx.segments))
+        o = ctx.buffer("mlstm.o", (rows, H * (V + 1)), torch.float32)
+        kernels.linear_recurrence(
+            proj[:, :self.col_k], proj[:, self.col_k:self.col_v], proj[:, self.col_v:self.col_g],
+            gates[:, :H], state, o, ctx.row_slot, seg, H, H, K, V + 1,
+            kernels.DECAY_SCALAR_INPUT, q_scale=K ** -0.5, n_requests=len(ctx.segments),
+            input_weight=gates[:, H:2 * H], ones=True)
+        gated = ctx.buffer("mlstm.gated", (rows, H * V))
+        kernels.memory_out_norm(o, gates[:, 2 * H:], proj[:, self.col_g:self.col_i],
+                                self.norm_weight, gated, H, V, self.eps, self.floor)
+        self.o_proj(gated, x, accumulate=accumulate)
+
+
 register_part("mixer", "gla", GatedLinearAttention, replace=True)
+register_part("mixer", "mlstm", MatrixMemory, replace=True)
 register_part("mixer", "mamba2", StateSpaceMixer, replace=True)
