@@ -393,9 +393,9 @@ def main() -> int:
                          "(default 1)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="qwen3-8b")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "vunasun"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "vunasun", "runidra"])
     ap.add_argument("--sizes", default="0.6b,8b",
-                    help="vunasun: the Qwen3 presets whose sizes both models take")
+                    help="vunasun, runidra: the Qwen3 presets whose sizes both models take")
     ap.add_argument("--layers", type=int, default=None, help="build fewer layers (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
@@ -433,6 +433,8 @@ def main() -> int:
     pk = peaks()
     if args.workload == "vunasun":
         return vunasun_workload(args)
+    if args.workload == "runidra":
+        return vunasun_workload(args, "runidra")
     cfg = preset_config(args.model, args.layers)
     full_layers = _full_layers(args.model)
     model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
@@ -449,11 +451,13 @@ def main() -> int:
         clocks.stop()
 
 
-def vunasun_workload(args) -> int:
-    """Prompt and decode rates of Vunasun models with random weights beside Qwen3 models of
-    the same width, feed-forward width, heads and number of layers (``--layers``, default 8;
-    ``--sizes``), and the design's own kernels one by one against the copy rate."""
-    from llmario_b200.benchmarks import vunasun as V
+def vunasun_workload(args, design: str = "vunasun") -> int:
+    """Prompt and decode rates of Vunasun (or Runidra) models with random weights beside Qwen3
+    models of the same width, feed-forward width, heads and number of layers (``--layers``,
+    default 8; ``--sizes``), and the design's own kernels one by one against the copy rate."""
+    import importlib
+
+    V = importlib.import_module("llmario_b200.benchmarks." + design)
 
     clocks = ClockSampler()
     clocks.start()
@@ -467,12 +471,12 @@ def vunasun_workload(args) -> int:
     finally:
         clocks.stop()
     first = rec["sizes"][next(iter(rec["sizes"]))]
-    line = {"metric": "decode tokens per second of a Vunasun model beside Qwen3 at equal sizes",
-            "value": first["vunasun"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps,
-            "warmup": warmup, "ms_per_step": first["vunasun"]["decode_ms"],
+    line = {"metric": f"decode tokens per second of a {design.capitalize()} model beside Qwen3 at equal sizes",
+            "value": first[design]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": first[design]["decode_ms"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (random weights, uniform random token ids)",
-            "config": {"workload": "vunasun", "layers": rec["layers"], "batch": rec["batch"],
+            "config": {"workload": design, "layers": rec["layers"], "batch": rec["batch"],
                        "prompt_len": rec["prompt_len"], "prefill_tokens": rec["prefill_tokens"],
                        "l2": "weights larger than L2 (steps); flushed (kernels)"},
             "clocks": clocks.summary(), "sizes": rec["sizes"], "kernels": rec["kernels"],

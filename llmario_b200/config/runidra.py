@@ -277,12 +277,13 @@ def sized_like(width: int, ff: int, heads: int, head_dim: int, layers: int, voca
     dense, latent attention + routed experts) on two residual streams.  The attention keeps a
     latent of 96 and a rotated part of 32 per token (one key row of 128; smaller for heads below
     64), queries through a latent of a quarter of the width; the memory has heads of 128 x 128
-    (at most half the width); the routed experts are
+    (at most half the width); at most 16 attention heads; the routed experts are
     `experts` of width ff / top with `top` chosen, beside a shared one of the same width."""
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top},
            "shared": {"ff": ff // top}}
     rot = min(32, head_dim // 2)
+    heads = min(heads, 16)      # the tensor-core decode kernels take up to 16 query heads per key head
     att = {"heads": heads, "dim": head_dim - rot, "rot_dim": rot, "vdim": head_dim,
            "q_rank": max(64, width // 4), "kv_rank": 128 - rot if head_dim >= 64 else 2 * head_dim,
            "scale": head_dim ** -0.5, "mask": {"size": window}, "rot": {"dims": rot, "base": 1e6}}

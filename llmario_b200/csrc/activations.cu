@@ -48,9 +48,11 @@ LLM_EXPORT int llm_gated_act(const float* gate_up, const float* bias, void* out,
   if (kind != ACT_SILU && kind != ACT_GELU_TANH) return LLM_ERR_ARGUMENT;
   const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
   if (out_dtype == LLM_F32)
-    return launch_pdl(gated_act_kernel<float>, blocks, 256, 0, stream, gate_up, bias, (float*)out, total, ff, kind);
+    return launched_many_blocks(
+        launch_pdl(gated_act_kernel<float>, blocks, 256, 0, stream, gate_up, bias, (float*)out, total, ff, kind), blocks);
   if (out_dtype == LLM_BF16)
-    return launch_pdl(gated_act_kernel<bf16>, blocks, 256, 0, stream, gate_up, bias, (bf16*)out, total, ff, kind);
+    return launched_many_blocks(
+        launch_pdl(gated_act_kernel<bf16>, blocks, 256, 0, stream, gate_up, bias, (bf16*)out, total, ff, kind), blocks);
   return LLM_ERR_UNSUPPORTED;
 }
 

@@ -257,11 +257,13 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 6) flash_paged_ke
   }
 }
 
-// out[row][head] = sum_z 2^(m_z - m*) o_z / sum_z 2^(m_z - m*) l_z   over the parts of a row
+// out[row][head] = sum_z 2^(m_z - m*) o_z / sum_z 2^(m_z - m*) l_z   over the parts of a row.
+// sink: a number per head that joins the sum below the line as one more part without an output,
+// exp(sink) (a key that takes weight and has no value); null: none.
 template <int HD>
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                              bf16* __restrict__ out, const int* __restrict__ rows, int Hq, int splits,
-                             float* __restrict__ clear, int clear_stride) {
+                             float* __restrict__ clear, int clear_stride, const float* __restrict__ sink) {
   pdl_trigger();
   pdl_wait();
   const int row = rows ? rows[blockIdx.x] : (int)blockIdx.x;
@@ -269,10 +271,12 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
   if (clear)      // the head's queries in the projection buffer, which every part has read by now
     for (int d = threadIdx.x; d < HD; d += blockDim.x)
       clear[(size_t)row * clear_stride + blockIdx.y * HD + d] = 0.f;
-  float mstar = -INFINITY;
+  // (the parts' maxima are base-2 logarithms: scores times scale times log2 e)
+  const float sk = sink ? sink[blockIdx.y] * 1.4426950408889634f : -INFINITY;
+  float mstar = sk;
   for (int z = 0; z < splits; ++z) mstar = fmaxf(mstar, part_ml[(rowhead * splits + z) * 2]);
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float acc = 0.f, lsum = 0.f;
+    float acc = 0.f, lsum = sink ? exp2f(sk - mstar) : 0.f;
     for (int z = 0; z < splits; ++z) {
       const float mz = part_ml[(rowhead * splits + z) * 2];
       if (mz == -INFINITY) continue;      // a part without keys: what lies in its place is not read
@@ -342,18 +346,26 @@ LLM_EXPORT int llm_attention_flash(const void* q, void* out, float* part_o, floa
   return LLM_ERR_UNSUPPORTED;
 }
 
+// Merge of the parts of split keys, with an optional sink per head (float32 [Hq]) in the sum.
+LLM_EXPORT int llm_attention_merge_sink(const float* part_o, const float* part_ml, void* out, const int* rows,
+                                        int n_rows, int Hq, int hd, int splits, float* clear, int clear_stride,
+                                        const float* sink, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  dim3 grid(n_rows, Hq);
+  if (hd == 128) return launch_pdl(merge_kernel<128>, grid, 128, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride, sink);
+  if (hd == 64) return launch_pdl(merge_kernel<64>, grid, 64, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride, sink);
+  if (hd == 32) return launch_pdl(merge_kernel<32>, grid, 32, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride, sink);
+  return LLM_ERR_UNSUPPORTED;
+}
+
 // Merge of the parts of split keys.  With clear given, also clear[row][head * hd .. + hd) = 0 for
 // every merged (row, head): the queries that llm_attention_decode_fused leaves in the projection
 // buffer when it splits the keys.
 LLM_EXPORT int llm_attention_merge_clear(const float* part_o, const float* part_ml, void* out,
                                          const int* rows, int n_rows, int Hq, int hd, int splits,
                                          float* clear, int clear_stride, cudaStream_t stream) {
-  if (n_rows <= 0) return 0;
-  dim3 grid(n_rows, Hq);
-  if (hd == 128) return launch_pdl(merge_kernel<128>, grid, 128, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride);
-  if (hd == 64) return launch_pdl(merge_kernel<64>, grid, 64, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride);
-  if (hd == 32) return launch_pdl(merge_kernel<32>, grid, 32, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride);
-  return LLM_ERR_UNSUPPORTED;
+  return llm_attention_merge_sink(part_o, part_ml, out, rows, n_rows, Hq, hd, splits, clear, clear_stride, nullptr,
+                                  stream);
 }
 
 LLM_EXPORT int llm_attention_merge(const float* part_o, const float* part_ml, void* out,

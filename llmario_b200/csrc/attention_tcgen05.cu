@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
     long long rows_per_page, int v_row_off, const bf16* __restrict__ k_cache,
     const bf16* __restrict__ v_cache, long long page_stride, bf16* __restrict__ out, const int* __restrict__ block_table, int table_stride,
     const int* __restrict__ items, int Hq, int Hkv, int page_size, float scale_log2, int window,
-    int* __restrict__ status) {
+    int* __restrict__ status, const float* __restrict__ sink) {
   constexpr int HALVES = HD / 64;
   constexpr uint32_t S_COLS = KT;              // fp32 scores of a tile
   constexpr uint32_t O_COL = 2 * S_COLS;       // first column of the output accumulator
@@ -403,6 +403,9 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
         tmem_ld_wait();
         l += __uint_as_float(other);
       }
+      // a sink joins the sum as exp(sink): one more key that has no value (m_used is a base-2
+      // logarithm, and finite for a row that sees its own key)
+      if (sink && rvalid) l += ex2(sink[head] * 1.4426950408889634f - m_used);
       if (done) {
         tc_fence_after();
         const float inv = 1.0f / l;
@@ -473,7 +476,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
     long long rows_per_page, int v_row_off, bf16* __restrict__ out, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ items, int n_items, int Hq, int Hkv, int page_size,
-    float scale_log2, int window, int* __restrict__ status) {
+    float scale_log2, int window, int* __restrict__ status, const float* __restrict__ sink) {
   constexpr int HALVES = HD / 64;
   constexpr uint32_t S_COLS = KT;
   constexpr uint32_t O_COL = 2 * S_COLS;
@@ -752,6 +755,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
       const uint32_t other = tmem_ld1(x_addr + (uint32_t)(4 + (half ^ 1)));
       tmem_ld_wait();
       l += __uint_as_float(other);
+      if (sink && rvalid) l += ex2(sink[head] * 1.4426950408889634f - m_used);
       const float inv = 1.0f / l;
       bf16* dst = out + ((size_t)(w.it.row_start + tok) * Hq + head) * HD + oc0;
       // the whole half row into registers, so that the next item's first P V need not wait for
@@ -814,7 +818,7 @@ template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long rows_per_page, int v_row_off,
            const bf16* kc, const bf16* vc, long long page_stride, bf16* out,
            const int* table, int table_stride, const int* items, int n_items, int Hq, int Hkv, int page_size,
-           float scale, int window, int persistent, int* status, cudaStream_t s) {
+           float scale, int window, int persistent, int* status, const float* sink, cudaStream_t s) {
   constexpr int smem = (int)sizeof(AttnStorage<HD>) + 1024;
   static_assert(smem <= 227 * 1024, "the Q tile and three stages of K and V fit one SM");
   if (tma_kv && persistent) {
@@ -835,7 +839,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long 
         pconf = true;
       }
       return launch_pdl(pk, dim3(sms), 320, smem, s, mq, mkv, rows_per_page, v_row_off, out, table, table_stride,
-                        items, n_items, Hq, Hkv, page_size, scale * 1.4426950408889634f, window, status);
+                        items, n_items, Hq, Hkv, page_size, scale * 1.4426950408889634f, window, status, sink);
     }
   }
   // keys and values by TMA leave warps 6-9 free: they take half of every row's softmax
@@ -848,7 +852,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long 
   }
   dim3 grid(n_items, Hkv);
   return launch_pdl(kernel, grid, 320, smem, s, mq, mkv, tma_kv, rows_per_page, v_row_off, kc, vc, page_stride, out,
-                    table, table_stride, items, Hq, Hkv, page_size, scale * 1.4426950408889634f, window, status);
+                    table, table_stride, items, Hq, Hkv, page_size, scale * 1.4426950408889634f, window, status, sink);
 }
 }  // namespace
 
@@ -860,12 +864,31 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long 
 // persistent: non-zero lets the kernel run, when K and V come by TMA and there are more (item, KV
 // head) pairs than SMs, as one CTA per SM that walks its share of the pairs; that pays while the
 // items are short (it saves about 3 us per pair) and costs a few percent when they are long.
+LLM_EXPORT int llm_attention_tcgen05_sink(const void* q, void* out, int rows, const void* k_cache,
+                                          const void* v_cache, long long page_stride, long long n_pages,
+                                          const int* block_table, int table_stride, const int* items,
+                                          int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
+                                          int window, int persistent, int* status, const float* sink,
+                                          cudaStream_t stream);
+
 LLM_EXPORT int llm_attention_tcgen05(const void* q, void* out, int rows, const void* k_cache,
                                      const void* v_cache, long long page_stride, long long n_pages,
                                      const int* block_table,
                                      int table_stride, const int* items, int n_items, int Hq, int Hkv,
                                      int hd, int page_size, float scale, int window, int persistent,
                                      int* status, cudaStream_t stream) {
+  return llm_attention_tcgen05_sink(q, out, rows, k_cache, v_cache, page_stride, n_pages, block_table,
+                                    table_stride, items, n_items, Hq, Hkv, hd, page_size, scale, window,
+                                    persistent, status, nullptr, stream);
+}
+
+// The same with a sink per query head (float32 [Hq], or null) in every row's softmax sum.
+LLM_EXPORT int llm_attention_tcgen05_sink(const void* q, void* out, int rows, const void* k_cache,
+                                          const void* v_cache, long long page_stride, long long n_pages,
+                                          const int* block_table, int table_stride, const int* items,
+                                          int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
+                                          int window, int persistent, int* status, const float* sink,
+                                          cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv) return LLM_ERR_ARGUMENT;
   const int G = Hq / Hkv;
@@ -890,8 +913,8 @@ LLM_EXPORT int llm_attention_tcgen05(const void* q, void* out, int rows, const v
   if (hd == 128)
     return launch<128>(mq, mkv, tma_kv, rows_per_page, v_row_off, (const bf16*)k_cache, (const bf16*)v_cache,
                        page_stride, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size, scale,
-                       window, persistent, status, stream);
+                       window, persistent, status, sink, stream);
   return launch<64>(mq, mkv, tma_kv, rows_per_page, v_row_off, (const bf16*)k_cache, (const bf16*)v_cache,
                     page_stride, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size, scale,
-                    window, persistent, status, stream);
+                    window, persistent, status, sink, stream);
 }

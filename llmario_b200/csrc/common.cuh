@@ -112,6 +112,15 @@ extern int g_llm_pdl;   // 1: launch with the programmatic-serialization attribu
 // sequence is therefore not launched that way by anyone, a part registered by a user included.
 extern int g_llm_after_rotation;
 
+// What the rotation kernel does for the reason above, for any kernel of many blocks that stands
+// directly in front of a product of many rows: called behind its launch, it makes a CTA-pair
+// product that follows wait for the kernel's end instead of starting as its programmatic
+// dependent.  (The chains of the first models are proven as they are and do not call it.)
+static inline int launched_many_blocks(int rc, long long blocks) {
+  if (blocks >= 512) g_llm_after_rotation = 1;
+  return rc;
+}
+
 // Launch a kernel that calls pdl_wait() itself.
 template <typename... KArgs, typename... Args>
 static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

@@ -50,11 +50,16 @@ struct alignas(1024) SharedStorage {
 };
 
 // grid: (feature tiles, token tiles, K splits).  Features per tile: 128, or 64 when gated.
+// Grouped form (tile_group given): W holds several matrices of group_rows rows one below the
+// other, and token tile y is multiplied with matrix tile_group[y] (a negative entry: the tile
+// holds no tokens and is left out).  The table is made by an earlier kernel of the step, so a
+// grouped launch waits for the kernels before it before it asks for its first weights.
 template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     const __grid_constant__ CUtensorMap map_c, int tma_out, TC* __restrict__ C, int ldc, int T, int N,
-    int K, int half, int interleaved, int* __restrict__ status) {
+    int K, int half, int interleaved, int* __restrict__ status, const int* __restrict__ tile_group,
+    int group_rows) {
   extern __shared__ uint8_t raw[];
   auto& sm = *reinterpret_cast<SharedStorage<BN, STAGES>*>(
       (reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -90,8 +95,16 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
+  int w_row0 = 0;          // first row of this tile's matrix inside W
+  bool live = nkb > 0;
+  if (tile_group) {
+    pdl_wait();
+    const int g = tile_group[blockIdx.y];
+    live = live && g >= 0;
+    w_row0 = g * group_rows;
+  }
 
-  if (nkb > 0) {
+  if (live) {
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- producer
       // The weights do not depend on any earlier kernel: the first ring of weight tiles is
@@ -102,16 +115,16 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
         const int k = (kb_begin + i) * TILE_K;
         if (EPI == EPI_GATED && interleaved) {
           // the matrix is stored with 16 gate rows, their 16 up rows, the next 16 gate rows, ...
-          tma_load_2d(sm.a[s], &map_w, k, 2 * n0, &sm.full[s]);
+          tma_load_2d(sm.a[s], &map_w, k, w_row0 + 2 * n0, &sm.full[s]);
         } else if (EPI == EPI_GATED) {
           // 16 gate rows, their 16 up rows, the next 16 gate rows, ...: every 32-lane quarter of
           // the accumulator then holds gate and up of the same 16 features
 #pragma unroll
           for (int b = 0; b < 8; ++b)
-            tma_load_2d(sm.a[s] + b * 16 * TILE_K * 2, &map_w, k, ((b & 1) ? half : 0) + n0 + (b >> 1) * 16,
-                        &sm.full[s]);
+            tma_load_2d(sm.a[s] + b * 16 * TILE_K * 2, &map_w, k,
+                        w_row0 + ((b & 1) ? half : 0) + n0 + (b >> 1) * 16, &sm.full[s]);
         } else {
-          tma_load_2d(sm.a[s], &map_w, k, n0, &sm.full[s]);
+          tma_load_2d(sm.a[s], &map_w, k, w_row0 + n0, &sm.full[s]);
         }
       };
       auto load_x = [&](int i) {
@@ -365,7 +378,8 @@ namespace {
 
 template <int BN, int STAGES, int EPI, typename TC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K, int half,
-           int splits, int interleaved, int* status, cudaStream_t stream) {
+           int splits, int interleaved, int* status, cudaStream_t stream, const int* tile_group = nullptr,
+           int group_rows = 0) {
   // the output goes through TMA when its rows are 16-byte multiples on a 16-byte aligned base
   CUtensorMap mc = mw;
   int tma_out = 0;
@@ -385,17 +399,18 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, 
   const int limit = EPI == EPI_GATED ? half : N;
   dim3 grid((limit + feat - 1) / feat, (T + BN - 1) / BN, splits);
   return launch_pdl(kernel, grid, 192, smem, stream, mw, mx, mc, tma_out, C, ldc, T, N, K, half, interleaved,
-                    status);
+                    status, tile_group, group_rows);
 }
 
 template <int EPI, typename TC>
 int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K,
-             int half, int splits, int interleaved, int* status, cudaStream_t stream) {
+             int half, int splits, int interleaved, int* status, cudaStream_t stream,
+             const int* tile_group = nullptr, int group_rows = 0) {
   switch (bn) {
-    case 16: return launch<16, 6, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
-    case 32: return launch<32, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
-    case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
-    case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
+    case 16: return launch<16, 6, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows);
+    case 32: return launch<32, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows);
+    case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows);
+    case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows);
   }
   return LLM_ERR_UNSUPPORTED;
 }
@@ -463,4 +478,36 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dty
     return LLM_ERR_UNSUPPORTED;
   }
   return LLM_ERR_ARGUMENT;
+}
+
+// The grouped product: W holds `groups` matrices [N][K] one below the other; the rows of X come in
+// tiles of `bn` (16, 32, 64 or 128) and tile y is multiplied with matrix tile_group[y] (device
+// int32 [ceil(T / bn)], made by an earlier kernel of the stream; a negative entry leaves the tile
+// out, its output rows are not written).  mode 0: C = X W_g^T (bf16 or f32); mode 2: W_g = [gate;
+// up] of `half` rows each and C = silu(gate) * up.  No split of K.
+LLM_EXPORT int llm_gemm_tcgen05_grouped(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
+                                        int lda, int ldw, int ldc, int mode, int half, int bn, int groups,
+                                        const int* tile_group, int* status, cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || groups <= 0) return 0;
+  if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return LLM_ERR_UNSUPPORTED;
+  if (((uintptr_t)X | (uintptr_t)W) & 15) return LLM_ERR_UNSUPPORTED;
+  if (!tile_group || (mode != 0 && mode != 2)) return LLM_ERR_ARGUMENT;
+  if (mode == 2 && (N != 2 * half || half % 16)) return LLM_ERR_UNSUPPORTED;   // (a box of 16 rows stays inside its matrix)
+  if ((long long)groups * N > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
+  CUtensorMap mw, mx;
+  if (!llm_tensor_map(W, (long long)groups * N, K, ldw, mode == 2 ? 16 : TILE_M, TILE_K, 0, &mw))
+    return LLM_ERR_UNSUPPORTED;
+  if (!llm_tensor_map(X, T, K, lda, bn, TILE_K, 0, &mx)) return LLM_ERR_UNSUPPORTED;
+  if (mode == 0) {
+    if (c_dtype == LLM_F32)
+      return dispatch<EPI_STORE, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, 1, 0, status, stream, tile_group, N);
+    if (c_dtype == LLM_BF16)
+      return dispatch<EPI_STORE, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, half, 1, 0, status, stream, tile_group, N);
+    return LLM_ERR_UNSUPPORTED;
+  }
+  if (c_dtype == LLM_BF16)
+    return dispatch<EPI_GATED, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, half, 1, 0, status, stream, tile_group, N);
+  if (c_dtype == LLM_F32)
+    return dispatch<EPI_GATED, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, 1, 0, status, stream, tile_group, N);
+  return LLM_ERR_UNSUPPORTED;
 }

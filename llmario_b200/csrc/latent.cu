@@ -103,15 +103,15 @@ LLM_EXPORT int llm_latent_store(const float* proj, int proj_stride, const float*
   if (rows <= 0) return 0;
   if (q_rank <= 0 || kv_rank <= 0 || rot_dim < 0 || 2 * rot_half > rot_dim) return LLM_ERR_ARGUMENT;
   if (dtype == LLM_F32)
-    return launch_pdl(latent_store_kernel<float>, rows, 128, 0, stream, proj, proj_stride, wq, wc,
+    return launched_many_blocks(launch_pdl(latent_store_kernel<float>, rows, 128, 0, stream, proj, proj_stride, wq, wc,
                       (const float2*)cos_sin, rot_half, (float*)cq_out, (float*)k_plane, (float*)v_plane,
                       page_stride, block_table, table_stride, row_slot, row_pos, page_size, q_rank, kv_rank,
-                      rot_dim, eps, write_cache);
+                      rot_dim, eps, write_cache), rows);
   if (dtype == LLM_BF16)
-    return launch_pdl(latent_store_kernel<bf16>, rows, 128, 0, stream, proj, proj_stride, wq, wc,
+    return launched_many_blocks(launch_pdl(latent_store_kernel<bf16>, rows, 128, 0, stream, proj, proj_stride, wq, wc,
                       (const float2*)cos_sin, rot_half, (bf16*)cq_out, (bf16*)k_plane, (bf16*)v_plane,
                       page_stride, block_table, table_stride, row_slot, row_pos, page_size, q_rank, kv_rank,
-                      rot_dim, eps, write_cache);
+                      rot_dim, eps, write_cache), rows);
   return LLM_ERR_UNSUPPORTED;
 }
 
@@ -123,10 +123,12 @@ LLM_EXPORT int llm_latent_query(const float* q, int q_stride, const float* cos_s
   if (2 * rot_half > rot_dim) return LLM_ERR_ARGUMENT;
   const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
   if (dtype == LLM_F32)
-    return launch_pdl(latent_query_kernel<float>, blocks, 256, 0, stream, q, q_stride, (const float2*)cos_sin,
-                      rot_half, (float*)q_plain, (float*)q_full, total, H, dim, rot_dim, kv_rank);
+    return launched_many_blocks(
+        launch_pdl(latent_query_kernel<float>, blocks, 256, 0, stream, q, q_stride, (const float2*)cos_sin, rot_half,
+                   (float*)q_plain, (float*)q_full, total, H, dim, rot_dim, kv_rank), blocks);
   if (dtype == LLM_BF16)
-    return launch_pdl(latent_query_kernel<bf16>, blocks, 256, 0, stream, q, q_stride, (const float2*)cos_sin,
-                      rot_half, (bf16*)q_plain, (bf16*)q_full, total, H, dim, rot_dim, kv_rank);
+    return launched_many_blocks(
+        launch_pdl(latent_query_kernel<bf16>, blocks, 256, 0, stream, q, q_stride, (const float2*)cos_sin, rot_half,
+                   (bf16*)q_plain, (bf16*)q_full, total, H, dim, rot_dim, kv_rank), blocks);
   return LLM_ERR_UNSUPPORTED;
 }

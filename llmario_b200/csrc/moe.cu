@@ -7,6 +7,14 @@
 // the form for steps of few rows, where a token's experts are read once each and nothing has
 // to be sorted; which expert a row uses is read on the device, so recorded steps replay.
 // Sums run in a fixed order per output, so a row's result does not depend on the batch.
+//
+// The grouped form, for 16-bit models on the tensor cores: the (token, chosen expert) pairs are
+// sorted by expert into a padded buffer in which every expert's rows start a tile of `bn` rows
+// (align), the tokens' inputs are copied there (gather), two grouped products
+// (llm_gemm_tcgen05_grouped: each tile of rows with its expert's matrices) make the gated
+// activation and the experts' outputs, and one pass sums a token's outputs with its weights
+// (combine).  Every expert in use is read once per tile of its rows, whatever the step's size;
+// all of it is decided on the device, so recorded steps replay.
 #include "common.cuh"
 
 namespace {
@@ -128,7 +136,105 @@ __global__ void __launch_bounds__(128) moe_down_rows_kernel(const T* __restrict_
     }
   }
 }
+// One block.  pos[i]: the row of pair i (token i / top, choice i % top) in the padded buffer;
+// tile_group[t]: the expert of tile t of that buffer, -1 for a tile without rows.  Which row of
+// its expert's range a pair gets depends on the order in which threads arrive; the result of a
+// row does not depend on where it stands.
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ ids, int n_pairs, int E, int bn,
+                                                         int n_tiles, int* __restrict__ pos,
+                                                         int* __restrict__ tile_group) {
+  extern __shared__ int sh[];       // counts[E], offsets[E], cursor[E]
+  int *counts = sh, *offsets = sh + E, *cursor = sh + 2 * E;
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0, cursor[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tile = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = tile * bn;
+      const int tiles = (counts[e] + bn - 1) / bn;
+      for (int t = 0; t < tiles && tile < n_tiles; ++t) tile_group[tile++] = e;
+    }
+    for (; tile < n_tiles; ++tile) tile_group[tile] = -1;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    pos[i] = (e >= 0 && e < E) ? offsets[e] + atomicAdd(&cursor[e], 1) : 0;
+  }
+}
+
+// xp[pos[i]][:] = h[i / top][:]
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ pos,
+                                                         T* __restrict__ xp, int width, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x;
+  const T* src = h + (size_t)(i / top) * width;
+  T* dst = xp + (size_t)pos[i] * width;
+  if ((width * sizeof(T)) % 16 == 0 && (((uintptr_t)h | (uintptr_t)xp) & 15) == 0) {
+    const int n = width * sizeof(T) / 16;
+    for (int j = threadIdx.x; j < n; j += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(src)[j];
+  } else {
+    for (int j = threadIdx.x; j < width; j += blockDim.x) dst[j] = src[j];
+  }
+}
+
+// y[r][c] (+)= sum_k wts[r][k] * d[pos[r * top + k]][c]  (+ sigmoid(gate[r]) * shared[r][c]), k ascending
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ d, const int* __restrict__ pos,
+                                                          const float* __restrict__ wts,
+                                                          const float* __restrict__ shared,
+                                                          const float* __restrict__ gate, int gate_stride,
+                                                          float* __restrict__ y, int width, int top, int accumulate) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float g = shared ? 1.f / (1.f + expf(-gate[(size_t)r * gate_stride])) : 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k)
+      sum = fmaf(wts[(size_t)r * top + k], d[(size_t)pos[(size_t)r * top + k] * width + c], sum);
+    if (shared) sum = fmaf(g, shared[(size_t)r * width + c], sum);
+    float* dst = y + (size_t)r * width + c;
+    *dst = accumulate ? *dst + sum : sum;
+  }
+}
 }  // namespace
+
+LLM_EXPORT int llm_moe_align(const int* ids, int n_pairs, int E, int bn, int n_tiles, int* pos, int* tile_group,
+                             cudaStream_t stream) {
+  if (n_pairs <= 0 || n_tiles <= 0) return 0;
+  if (E <= 0 || E > 4096 || bn <= 0) return LLM_ERR_UNSUPPORTED;
+  return launch_pdl(moe_align_kernel, 1, 1024, (size_t)3 * E * sizeof(int), stream, ids, n_pairs, E, bn, n_tiles,
+                    pos, tile_group);
+}
+
+LLM_EXPORT int llm_moe_gather(const void* h, const int* pos, void* xp, int dtype, int n_pairs, int width, int top,
+                              cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (dtype == LLM_F32)
+    return launch_pdl(moe_gather_kernel<float>, n_pairs, 128, 0, stream, (const float*)h, pos, (float*)xp, width, top);
+  if (dtype == LLM_BF16)
+    return launch_pdl(moe_gather_kernel<bf16>, n_pairs, 128, 0, stream, (const bf16*)h, pos, (bf16*)xp, width, top);
+  return LLM_ERR_UNSUPPORTED;
+}
+
+LLM_EXPORT int llm_moe_combine(const float* d, const int* pos, const float* wts, const float* shared,
+                               const float* gate, int gate_stride, float* y, int rows, int width, int top,
+                               int accumulate, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (shared && !gate) return LLM_ERR_ARGUMENT;
+  return launched_many_blocks(launch_pdl(moe_combine_kernel, rows, 256, 0, stream, d, pos, wts, shared, gate,
+                                         gate_stride, y, width, top, accumulate), rows);
+}
 
 LLM_EXPORT int llm_moe_route(const float* z, int z_stride, int rows, int E, int top, int* ids, float* wts,
                              cudaStream_t stream) {

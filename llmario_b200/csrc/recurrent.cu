@@ -635,11 +635,13 @@ LLM_EXPORT int llm_memory_out_norm(const float* o, int o_stride, const float* m,
   if (items <= 0 || V <= 0) return 0;
   const int blocks = (int)((items + 3) / 4);
   if (out_dtype == LLM_F32)
-    return launch_pdl(memory_out_norm_kernel<float>, blocks, 128, 0, stream, o, o_stride, m, m_stride, g,
-                      g_stride, w, (float*)out, out_stride, items, H, V, eps, floor_);
+    return launched_many_blocks(launch_pdl(memory_out_norm_kernel<float>, blocks, 128, 0, stream, o, o_stride, m,
+                                           m_stride, g, g_stride, w, (float*)out, out_stride, items, H, V, eps,
+                                           floor_), blocks);
   if (out_dtype == LLM_BF16)
-    return launch_pdl(memory_out_norm_kernel<bf16>, blocks, 128, 0, stream, o, o_stride, m, m_stride, g,
-                      g_stride, w, (bf16*)out, out_stride, items, H, V, eps, floor_);
+    return launched_many_blocks(launch_pdl(memory_out_norm_kernel<bf16>, blocks, 128, 0, stream, o, o_stride, m,
+                                           m_stride, g, g_stride, w, (bf16*)out, out_stride, items, H, V, eps,
+                                           floor_), blocks);
   return LLM_ERR_UNSUPPORTED;
 }
 

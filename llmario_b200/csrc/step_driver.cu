@@ -86,6 +86,13 @@ int llm_attention_tcgen05(const void* q, void* out, int rows, const void* k_cach
                           long long page_stride, long long n_pages, const int* block_table, int table_stride,
                           const int* items, int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
                           int window, int persistent, int* status, cudaStream_t stream);
+int llm_attention_tcgen05_sink(const void* q, void* out, int rows, const void* k_cache, const void* v_cache,
+                               long long page_stride, long long n_pages, const int* block_table, int table_stride,
+                               const int* items, int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
+                               int window, int persistent, int* status, const float* sink, cudaStream_t stream);
+int llm_attention_merge_sink(const float* part_o, const float* part_ml, void* out, const int* rows, int n_rows,
+                             int Hq, int hd, int splits, float* clear, int clear_stride, const float* sink,
+                             cudaStream_t stream);
 int llm_kv_gather(const void* k_src, const void* v_src, long long src_page_stride, const int* block_table,
                   int table_stride, int page_size, void* k_dst, void* v_dst, long long dst_page_stride,
                   int dst_page_size, int Hkv, int hd, int dtype, const int* items, int n_items,
@@ -255,7 +262,7 @@ Arena& arena() {
 struct Plan {          // the rows of the step as work items for one (group, large_cap)
   int group = 0, large_cap = 0;
   int n_small = 0, n_large = 0;
-  bool small_single = false;
+  bool small_single = false, single_small = false;
   const int* small = nullptr;       // device quadruples (first row, tokens, slot, first position)
   const int* large = nullptr;
   const int* small_rows = nullptr;  // the rows of the small items, for the merge
@@ -349,14 +356,18 @@ struct Run {
     return 0;
   }
 
-  int plan_for(int group, int large_cap, const Plan** out) {
+  // single_small: only items of one token count as small (their keys can then always be cut
+  // into parts and merged); every longer item is a large one
+  int plan_for(int group, int large_cap, const Plan** out, bool single_small = false) {
     if (large_cap < 1) large_cap = 1;
     for (const Plan& p : plans)
-      if (p.group == group && p.large_cap == large_cap) { *out = &p; return 0; }
+      if (p.group == group && p.large_cap == large_cap && p.single_small == single_small) { *out = &p; return 0; }
     Plan p;
     p.group = group;
     p.large_cap = large_cap;
-    const int small_cap = (group <= 8 ? 8 : 16) / group < 1 ? 1 : (group <= 8 ? 8 : 16) / group;
+    p.single_small = single_small;
+    const int small_cap = single_small ? 1
+                          : (group <= 8 ? 8 : 16) / group < 1 ? 1 : (group <= 8 ? 8 : 16) / group;
     if (st.all_single) {
       p.n_small = st.rows;
       p.small_single = true;
@@ -501,29 +512,34 @@ struct Run {
   int attention(const LlmLayerDesc& L, const LlmCallDesc& c, const void* q, void* out) {
     const int Hq = L.num_heads, Hkv = L.num_kv_heads, hd = L.head_dim, group = Hq / Hkv;
     const int window = L.window;
-    // (a sink in the softmax's sum, or values that are a prefix of their keys: the generic kernel)
-    const bool plain = L.sink == nullptr && (L.value_dim == 0 || L.value_dim == hd);
-    if (!plain || st.dtype != LLM_BF16 || !(hd == 32 || hd == 64 || hd == 128) || group > 16)
+    // Values that are a prefix of their keys go to the generic kernel.  A sink in the softmax's
+    // sum is known to the generic kernel, to the tcgen05 kernel of long portions, and to the merge
+    // of split keys (the keys of short items are then always cut into at least two parts, so that
+    // the merge runs); other kernels are not chosen for a layer with a sink.
+    const bool whole_values = L.value_dim == 0 || L.value_dim == hd;
+    const int ps = c.page_size;
+    const bool tc = (hd == 64 || hd == 128) && 128 % group == 0 && (c.page_stride * 2) % 16 == 0;
+    if (!whole_values || st.dtype != LLM_BF16 || !(hd == 32 || hd == 64 || hd == 128) || group > 16 ||
+        (L.sink != nullptr && !tc))
       return check(llm_attention_generic(q, out, c.k, c.v, st.dtype, c.page_stride, c.block_table,
                                          c.table_stride, st.row_slot, st.row_pos, st.rows, Hq, Hkv, hd,
                                          c.page_size, L.scale, window, L.sink, L.value_dim, stream), K_GENERIC);
-    const int ps = c.page_size;
-    const bool tc = (hd == 64 || hd == 128) && 128 % group == 0 && (c.page_stride * 2) % 16 == 0;
-    const bool x2 = tc && ps >= 32 && (ps & (ps - 1)) == 0 && c.storage != nullptr && ps < 64 &&
+    const bool x2 = tc && L.sink == nullptr && ps >= 32 && (ps & (ps - 1)) == 0 && c.storage != nullptr && ps < 64 &&
                     (long long)st.rows * Hkv >= 4LL * sm_count() * (128 / group);
     const Plan* plan = nullptr;
-    int rc = plan_for(group, (x2 ? 256 : tc ? 128 : 64) / group, &plan);
+    int rc = plan_for(group, (x2 ? 256 : tc ? 128 : 64) / group, &plan, L.sink != nullptr);
     if (rc) return rc;
     const int reach = reach_of(window, st.max_pos);
     if (plan->n_small) {
       const bool tma = group <= 8 && decode_tma_ok(c, hd);
-      const int splits = plan->small_single
-                             ? llm_decode_splits(plan->n_small, Hkv, reach, (tma ? DECODE_TMA_CTAS_PER_SM : 6) * sm_count(),
-                                                 tma ? DECODE_TMA_TILE : 32)
-                             : 1;
+      int splits = plan->small_single
+                       ? llm_decode_splits(plan->n_small, Hkv, reach, (tma ? DECODE_TMA_CTAS_PER_SM : 6) * sm_count(),
+                                           tma ? DECODE_TMA_TILE : 32)
+                       : 1;
+      if (L.sink != nullptr && splits < 2) splits = 2;      // the sink joins the sum in the merge
       float *part_o, *part_ml;
       const int resident = DECODE_TMA_CTAS_PER_SM * sm_count();
-      if (g_persistent_decode && tma && plan->small == nullptr && st.rows <= PERSISTENT_MAX_ROWS &&
+      if (g_persistent_decode && L.sink == nullptr && tma && plan->small == nullptr && st.rows <= PERSISTENT_MAX_ROWS &&
           (long long)plan->n_small * Hkv * splits > resident &&
           (long long)plan->n_small * Hkv * splits <= (long long)PERSISTENT_MAX_WAVES * resident) {
         rc = parts(PERSISTENT_PARTS, L, &part_o, &part_ml);
@@ -554,8 +570,8 @@ struct Run {
                                        16, Hq, Hkv, hd, ps, L.scale, window, splits, stream), K_FLASH);
       if (rc) return rc;
       if (splits > 1) {
-        rc = check(llm_attention_merge_clear(part_o, part_ml, out, plan->small_rows, plan->n_small, Hq, hd,
-                                             splits, nullptr, 0, stream), K_MERGE);
+        rc = check(llm_attention_merge_sink(part_o, part_ml, out, plan->small_rows, plan->n_small, Hq, hd,
+                                            splits, nullptr, 0, L.sink, stream), K_MERGE);
         if (rc) return rc;
       }
     }
@@ -584,19 +600,19 @@ struct Run {
                                    Hkv, hd, LLM_BF16, gp->list, gp->n_requests, gp->total_chunks, stream),
                      K_KV_GATHER);
           if (rc) return rc;
-          rc = check(llm_attention_tcgen05(q, out, st.rows, ks, vs, stride, gp->scratch_pages, gp->table,
-                                           gp->table_stride, gp->gathered, gp->n_gathered, Hq, Hkv, hd, D, L.scale,
-                                           window, persistent, st.status, stream), K_TCGEN05);
+          rc = check(llm_attention_tcgen05_sink(q, out, st.rows, ks, vs, stride, gp->scratch_pages, gp->table,
+                                                gp->table_stride, gp->gathered, gp->n_gathered, Hq, Hkv, hd, D, L.scale,
+                                                window, persistent, st.status, L.sink, stream), K_TCGEN05);
           if (rc) return rc;
           direct = gp->direct;
           n_direct = gp->n_direct;
         }
       }
       if (n_direct == 0) return 0;
-      return check(llm_attention_tcgen05(q, out, st.rows, c.k, c.v, c.page_stride,
-                                         c.storage != nullptr ? c.n_pages : 0, c.block_table, c.table_stride,
-                                         direct, n_direct, Hq, Hkv, hd, ps, L.scale, window, persistent,
-                                         st.status, stream), K_TCGEN05);
+      return check(llm_attention_tcgen05_sink(q, out, st.rows, c.k, c.v, c.page_stride,
+                                              c.storage != nullptr ? c.n_pages : 0, c.block_table, c.table_stride,
+                                              direct, n_direct, Hq, Hkv, hd, ps, L.scale, window, persistent,
+                                              st.status, L.sink, stream), K_TCGEN05);
     }
     if (plan->n_large)
       return check(llm_attention_flash(q, out, nullptr, nullptr, c.k, c.v, c.page_stride, c.block_table,

@@ -109,7 +109,7 @@ template <typename TOut>
 int launch_step(const StreamArgs& p, void* out, int rows, cudaStream_t stream) {
   const int threads = p.width >= 1024 ? 256 : 128;
 #define STEP(N) \
-  case N: return launch_pdl(stream_step_kernel<TOut, N>, rows, threads, 0, stream, p, (TOut*)out)
+  case N: return launched_many_blocks(launch_pdl(stream_step_kernel<TOut, N>, rows, threads, 0, stream, p, (TOut*)out), rows)
   switch (p.S) {
     STEP(1); STEP(2); STEP(3); STEP(4); STEP(5); STEP(6); STEP(7); STEP(8);
   }

@@ -187,6 +187,17 @@ def describe_step(ctx, x: Optional[torch.Tensor] = None) -> StepDesc:
 _launches = c_int(0)
 
 
+def tensor_core_attention(dtype: torch.dtype, view, num_heads: int, num_kv_heads: int,
+                          head_dim: int) -> bool:
+    """Whether :func:`attention` serves such a layer with the tensor-core kernels also when it
+    has a sink: bfloat16, a head size of 64 or 128, a group of query heads that divides 128 and
+    is at most 16 (the rule of ``Run::attention`` in ``csrc/step_driver.cu``).  Those kernels
+    read and write whole value rows."""
+    group = num_heads // num_kv_heads
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 16 and 128 % group == 0
+            and (view.page_stride * 2) % 16 == 0)
+
+
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
               head_dim: int, scale: float, window: Optional[int],
               sink: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> None:

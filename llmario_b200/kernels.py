@@ -58,6 +58,8 @@ def _signatures():
         "llm_attention_flash": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "llm_attention_merge": [P, P, P, P, I, I, I, I, P],
         "llm_attention_merge_clear": [P, P, P, P, I, I, I, I, P, I, P],
+        "llm_attention_merge_sink": [P, P, P, P, I, I, I, I, P, I, P, P],
+        "llm_attention_tcgen05_sink": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, I, P, P, P],
         "llm_attention_decode_fused": [P, I, P, P, P, P, L, I, I, P, P, L, P, I, P, P, I, P, P, P,
                                        F, I, I, I, I, I, F, I, I, P, P],
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
@@ -87,6 +89,10 @@ def _signatures():
         "llm_latent_query": [P, I, P, I, P, P, I, I, I, I, I, I, P],
         "llm_gemm_simt_batched": [P, P, P, I, I, I, I, I, I, I, I, I, L, L, L, P],
         "llm_moe_route": [P, I, I, I, I, P, P, P],
+        "llm_moe_align": [P, I, I, I, I, P, P, P],
+        "llm_moe_gather": [P, P, P, I, I, I, I, P],
+        "llm_moe_combine": [P, P, P, P, P, I, P, I, I, I, I, P],
+        "llm_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, P],
         "llm_moe_gate_up_rows": [P, P, P, P, I, I, I, I, I, P],
         "llm_moe_down_rows": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, P],
         "llm_causal_conv_silu": [P, I, P, P, P, L, P, P, I, I, I, P, I, I, I, P],
@@ -1123,19 +1129,25 @@ def latent_query(q: torch.Tensor, cos_sin: Optional[torch.Tensor], q_plain: torc
                                   _stream()), "latent_query")
 
 
+HEAD_LINEAR_SIMT_ROWS = 128     # up to so many rows the per-head maps are one CUDA-core launch
+
+
 def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """A map per head: ``out[r, h, :] = w[h] @ a[r, h, :]``.  a [rows, H, in] and out
     [rows, H, out_features] may be views with a row stride and a head stride (the last dimension dense); w
-    [H, out_features, in] contiguous.  bfloat16 operands whose rows are whole 16-byte units go to
-    the tensor-core product head by head, everything else to one batched CUDA-core launch."""
+    [H, out_features, in] contiguous.  Many rows of bfloat16 operands whose rows are whole
+    16-byte units go to the tensor-core product head by head; few rows (a launch per head would
+    cost more than the arithmetic) and everything else to one batched CUDA-core launch."""
     _cuda(a, w, out)
     rows, H, k = a.shape
     n = w.shape[1]
     assert w.shape == (H, n, k) and w.is_contiguous() and out.shape == (rows, H, n)
     assert a.stride(2) == 1 and out.stride(2) == 1 and a.dtype == w.dtype
-    if all(_tc_ok(a[:, h], w[h], out[:, h]) for h in range(H)):
+    if rows > HEAD_LINEAR_SIMT_ROWS and all(_tc_ok(a[:, h], w[h], out[:, h]) for h in range(H)):
+        # (the one-CTA kernel also for many rows: a head's product is small, and CTA-pair
+        # products are never launched one directly behind the other)
         for h in range(H):
-            gemm_tcgen05(a[:, h], w[h], out[:, h], 0)
+            gemm_tcgen05(a[:, h], w[h], out[:, h], 0, bn=128)
         return
     _check(lib().llm_gemm_simt_batched(_ptr(a), _ptr(w), _ptr(out), _dt(a), _dt(out), rows, n, k,
                                        a.stride(0), k, out.stride(0), H, a.stride(1), n * k,
@@ -1186,3 +1198,71 @@ def moe_down_rows(act: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, wts:
                                    shared_gate.stride(0) if shared_gate is not None else 0,
                                    _ptr(y), _dt(act), rows, width, ff, top, int(accumulate),
                                    _stream()), "moe_down_rows")
+
+
+def moe_grouped_ok(h_dtype: torch.dtype, width: int, ff: int) -> bool:
+    """Whether the routed experts of these sizes run as grouped tensor-core products."""
+    return h_dtype == torch.bfloat16 and width % 8 == 0 and ff % 16 == 0
+
+
+def moe_tile(pairs: int, experts: int) -> int:
+    """Rows of a tile of the padded buffer: the smallest tile that holds an expert's average share."""
+    share = -(-pairs // experts)
+    for bn in (16, 32, 64):
+        if share <= bn:
+            return bn
+    return 128
+
+
+def moe_align(ids: torch.Tensor, experts: int, bn: int, pos: torch.Tensor,
+              tile_group: torch.Tensor) -> None:
+    """Sort the (row, choice) pairs of ``ids`` by expert: ``pos`` (int32 [pairs]) is each pair's
+    row in a buffer in which every expert's rows start a tile of ``bn`` rows, ``tile_group``
+    (int32 [tiles], tiles >= pairs / bn + experts) the expert of every tile or -1."""
+    _cuda(ids, pos, tile_group)
+    assert ids.dtype == pos.dtype == tile_group.dtype == torch.int32
+    assert ids.is_contiguous() and pos.numel() == ids.numel()
+    assert tile_group.numel() * bn >= ids.numel() + experts * (bn - 1)
+    _check(lib().llm_moe_align(_ptr(ids), ids.numel(), experts, bn, tile_group.numel(), _ptr(pos),
+                               _ptr(tile_group), _stream()), "moe_align")
+
+
+def moe_gather(h: torch.Tensor, pos: torch.Tensor, xp: torch.Tensor, top: int) -> None:
+    """xp[pos[i]] = h[i // top]."""
+    _cuda(h, pos, xp)
+    assert h.is_contiguous() and xp.is_contiguous() and h.dtype == xp.dtype
+    assert h.shape[1] == xp.shape[1] and pos.numel() == h.shape[0] * top
+    _check(lib().llm_moe_gather(_ptr(h), _ptr(pos), _ptr(xp), _dt(h), pos.numel(), h.shape[1], top,
+                                _stream()), "moe_gather")
+
+
+def moe_combine(d: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, y: torch.Tensor,
+                accumulate: bool, shared: Optional[torch.Tensor] = None,
+                shared_gate: Optional[torch.Tensor] = None) -> None:
+    """y[r] (+)= sum_k wts[r, k] d[pos[r, k]] (+ sigmoid(shared_gate[r]) shared[r])."""
+    _cuda(d, pos, wts, y, shared, shared_gate)
+    rows, top = wts.shape
+    width = y.shape[1]
+    assert d.dtype == y.dtype == wts.dtype == torch.float32 and d.is_contiguous()
+    assert y.is_contiguous() and d.shape[1] == width and pos.numel() == rows * top
+    if shared is not None:
+        assert shared.dtype == torch.float32 and shared.is_contiguous()
+    _check(lib().llm_moe_combine(_ptr(d), _ptr(pos), _ptr(wts), _ptr(shared), _ptr(shared_gate),
+                                 shared_gate.stride(0) if shared_gate is not None else 0, _ptr(y),
+                                 rows, width, top, int(accumulate), _stream()), "moe_combine")
+
+
+def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,
+                 bn: int, gated: bool) -> None:
+    """The tensor-core product with a matrix per tile of ``bn`` rows of ``a``: tile t uses
+    ``w[tile_group[t]]`` (w [groups, N, K] bfloat16; a negative entry leaves the tile out).
+    ``gated``: w[g] = [gate; up] and out = silu(a gate^T) * (a up^T) ([rows, N / 2])."""
+    _cuda(a, w, out, tile_group)
+    T, K = a.shape
+    G, N, _ = w.shape
+    assert a.dtype == w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
+    assert out.stride(1) == 1 and tile_group.numel() * bn >= T
+    _check(lib().llm_gemm_tcgen05_grouped(_ptr(a), _ptr(w), _ptr(out), _dt(out), T, N, K,
+                                          a.stride(0), K, out.stride(0), 2 if gated else 0,
+                                          N // 2 if gated else 0, bn, G, _ptr(tile_group),
+                                          _ptr(tc_status(a.device)), _stream()), "gemm_grouped")

@@ -116,6 +116,7 @@ class GatedFeedForward:
 
 class RoutedExperts:
     graph_safe = True      # which experts a row uses is read on the device
+    grouped = True         # (False: always the row-wise kernels; for comparisons)
 
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
         self.hidden = W = int(spec["hidden_size"])
@@ -158,13 +159,29 @@ class RoutedExperts:
         ids = ctx.buffer("moe.ids", (rows, top), torch.int32)
         wts = ctx.buffer("moe.weights", (rows, top), torch.float32)
         kernels.moe_route(z, E, top, ids, wts)
-        act = ctx.buffer("moe.act", (rows, top, self.ff))
-        kernels.moe_gate_up_rows(h, self.gate_up, ids, act)
         shared = gate = None
         if self.shared is not None:
             shared = ctx.buffer("moe.shared", (rows, self.hidden), torch.float32)
             self.shared.forward(ctx, h, shared, accumulate=False)
             gate = z[:, E]
+        if kernels.moe_grouped_ok(h.dtype, self.hidden, self.ff) and self.grouped:
+            # sorted by expert into tiles of rows, two grouped tensor-core products, one sum
+            pairs = rows * top
+            bn = kernels.moe_tile(pairs, E)
+            tiles = -(-pairs // bn) + E
+            pos = ctx.buffer("moe.pos", (pairs,), torch.int32)
+            tile_group = ctx.buffer("moe.tiles", (tiles,), torch.int32)
+            kernels.moe_align(ids, E, bn, pos, tile_group)
+            xp = ctx.buffer("moe.x", (tiles * bn, self.hidden))
+            kernels.moe_gather(h, pos, xp, top)
+            act = ctx.buffer("moe.act", (tiles * bn, self.ff))
+            kernels.gemm_grouped(xp, self.gate_up, act, tile_group, bn, gated=True)
+            d = ctx.buffer("moe.down", (tiles * bn, self.hidden), torch.float32)
+            kernels.gemm_grouped(act, self.down, d, tile_group, bn, gated=False)
+            kernels.moe_combine(d, pos, wts, x, accumulate, shared, gate)
+            return
+        act = ctx.buffer("moe.act", (rows, top, self.ff))
+        kernels.moe_gate_up_rows(h, self.gate_up, ids, act)
         kernels.moe_down_rows(act, self.down, ids, wts, x, accumulate, shared, gate)
 
 

@@ -98,11 +98,17 @@ class LatentAttention:
         kernels.latent_query(q, angles, q_plain, q_full, H, D, R, C)
         kernels.head_linear(q_plain.view(rows, H, D), self.key_maps,
                             q_full.view(rows, H, self.key_dim)[:, :, :C])
-        mixed = ctx.buffer("latent.mixed", (rows, H * C))        # sum_j p_j c_j per head
+        # sum_j p_j c_j per head.  The tensor-core kernels work on whole value rows (what lies
+        # behind the latent in a value row of the cache is zero and never written); the generic
+        # kernel is told to stop at the latent's end.
+        whole = driver.tensor_core_attention(ctx.dtype, view, H, 1, self.key_dim)
+        vd = self.key_dim if whole else C
+        mixed = ctx.buffer("latent.mixed", (rows, H * vd))
         driver.attention(ctx, q_full, mixed, view, H, 1, self.key_dim, self.scale, self.mask,
-                         sink=self.sink, value_dim=C)
+                         sink=self.sink, value_dim=None if whole else C)
         out = ctx.buffer("latent.out", (rows, H * V))
-        kernels.head_linear(mixed.view(rows, H, C), self.value_maps, out.view(rows, H, V))
+        kernels.head_linear(mixed.view(rows, H, vd)[:, :, :C], self.value_maps,
+                            out.view(rows, H, V))
         self.o_proj(out, x, accumulate=accumulate)
 
 

@@ -132,10 +132,15 @@ def expert_ff(h, t, p: str):
     return (silu(h @ t[p + "gate"].T) * (h @ t[p + "up"].T)) @ t[p + "down"].T
 
 
-def routed_ff(h, t, p: str, mlp: dict):
+def routed_ff(h, t, p: str, mlp: dict, margins: Optional[list] = None):
+    """``margins`` collects, per token, how far the last chosen logit lies above the best one
+    that was not chosen (a close call there decides which expert runs)."""
     n, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
     z = h @ t[p + "router"].T + t[p + "router.b"]
     out = np.zeros((h.shape[0], t[p + "e0.down"].shape[0]), F)
+    if margins is not None and top < n:
+        ordered = -np.sort(-z, axis=1)
+        margins.append(ordered[:, top - 1] - ordered[:, top])
     for i in range(h.shape[0]):
         chosen = np.argsort(-z[i], kind="stable")[:top]
         w = np.exp(z[i][chosen] - z[i][chosen].max())
@@ -148,8 +153,10 @@ def routed_ff(h, t, p: str, mlp: dict):
     return out
 
 
-def feed_forward(h, t, p: str, mlp: dict):
-    return dense_ff(h, t, p) if mlp.get("kind", "dense") == "dense" else routed_ff(h, t, p, mlp)
+def feed_forward(h, t, p: str, mlp: dict, margins: Optional[list] = None):
+    if mlp.get("kind", "dense") == "dense":
+        return dense_ff(h, t, p)
+    return routed_ff(h, t, p, mlp, margins)
 
 
 # --------------------------------------------------------------------------------------------
@@ -162,9 +169,11 @@ def run_order(cfg: dict) -> List[int]:
     return list(range(a)) + list(range(a, b)) * times + list(range(b, n))
 
 
-def forward(cfg: dict, tensors: Dict[str, np.ndarray], tokens, layers_out: Optional[list] = None):
+def forward(cfg: dict, tensors: Dict[str, np.ndarray], tokens, layers_out: Optional[list] = None,
+            margins: Optional[list] = None):
     """Logits [T, vocab] of a whole sequence from position 0.  ``layers_out`` collects the
-    residual stream (the sum of the streams) behind every layer run."""
+    residual stream (the sum of the streams) behind every layer run, ``margins`` the routers'
+    margins per token (see :func:`routed_ff`), one array per routed layer run."""
     t = {k: np.asarray(v, F) for k, v in tensors.items()}
     eps = float(cfg["norm"]["eps"])
     x0 = t["embed"][np.asarray(tokens)]
@@ -176,7 +185,7 @@ def forward(cfg: dict, tensors: Dict[str, np.ndarray], tokens, layers_out: Optio
         subs = [("1", lambda a, L=layer, P=p: (mlstm_mixer if L["type"] == "mlstm" else
                                                 latent_attention_mixer)(a, t, P + "mix.", L["mixer"], eps))]
         if layer.get("mlp") is not None:
-            subs.append(("2", lambda a, L=layer, P=p: feed_forward(a, t, P + "mlp.", L["mlp"])))
+            subs.append(("2", lambda a, L=layer, P=p: feed_forward(a, t, P + "mlp.", L["mlp"], margins)))
         for q, fn in subs:
             if streams:
                 cin, cout, mix = t[f"{p}hc{q}.in"], t[f"{p}hc{q}.out"], t[f"{p}hc{q}.mix"]
