@@ -58,6 +58,74 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   }
 }
 
+
+// Router logits and the choice in one kernel, one block per row: the row of h is staged in shared
+// memory in 32-bit, every warp makes logits z[e] = w[e] . h + b[e] (w and b 32-bit, sums in a
+// fixed order), then warp 0 chooses as moe_route_kernel does.  Rows of w behind the E experts'
+// (n_out - E of them: the gate of a shared expert) get their logits too; all go to z_out.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h, const float* __restrict__ w,
+                                                         const float* __restrict__ b, float* __restrict__ z_out,
+                                                         int z_stride, int width, int E, int n_out, int top,
+                                                         int* __restrict__ ids, float* __restrict__ wts) {
+  extern __shared__ float rs[];        // h[width], z[n_out]
+  float* h_s = rs;
+  float* z_s = rs + width;
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) h_s[i] = to_f32(h[(size_t)r * width + i]);
+  __syncthreads();
+  for (int e = warp; e < n_out; e += nwarps) {
+    const float* we = w + (size_t)e * width;
+    float acc = 0.f;
+    if ((width & 3) == 0 && ((uintptr_t)we & 15) == 0) {
+      for (int i = lane * 4; i < width; i += 128) {
+        const float4 a = *reinterpret_cast<const float4*>(we + i);
+        acc = fmaf(a.x, h_s[i], acc), acc = fmaf(a.y, h_s[i + 1], acc);
+        acc = fmaf(a.z, h_s[i + 2], acc), acc = fmaf(a.w, h_s[i + 3], acc);
+      }
+    } else {
+      for (int i = lane; i < width; i += 32) acc = fmaf(we[i], h_s[i], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const float v = acc + (b ? b[e] : 0.f);
+      z_s[e] = v;
+      z_out[(size_t)r * z_stride + e] = v;
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float best[MAX_TOP];
+  int pick[MAX_TOP];
+  for (int k = 0; k < top; ++k) {
+    float v = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= pick[j] == e;
+      const float x = z_s[e];
+      if (!taken && (x > v || (x == v && e < at) || at == 0x7fffffff)) v = x, at = e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (oa != 0x7fffffff && (at == 0x7fffffff || ov > v || (ov == v && oa < at))) v = ov, at = oa;
+    }
+    best[k] = v, pick[k] = at;
+  }
+  if (lane == 0) {
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) sum += expf(best[k] - best[0]);
+    for (int k = 0; k < top; ++k) {
+      ids[(size_t)r * top + k] = pick[k];
+      wts[(size_t)r * top + k] = expf(best[k] - best[0]) / sum;
+    }
+  }
+}
+
 template <typename T> __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x,
                                                                int n, int lane);
 template <> __device__ __forceinline__ float dot_row<float>(const float* __restrict__ w, const float* __restrict__ x,
@@ -234,6 +302,30 @@ LLM_EXPORT int llm_moe_combine(const float* d, const int* pos, const float* wts,
   if (shared && !gate) return LLM_ERR_ARGUMENT;
   return launched_many_blocks(launch_pdl(moe_combine_kernel, rows, 256, 0, stream, d, pos, wts, shared, gate,
                                          gate_stride, y, width, top, accumulate), rows);
+}
+
+// The router: z_out[r][0:n_out] = w h_r + b (w float32 [n_out][width], the first E rows the
+// experts'), ids / wts the `top` chosen experts of every row and their weights.
+LLM_EXPORT int llm_moe_router(const void* h, int dtype, const float* w, const float* b, float* z_out, int z_stride,
+                              int rows, int width, int E, int n_out, int top, int* ids, float* wts,
+                              cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (top < 1 || top > MAX_TOP || top > E || n_out < E) return LLM_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)(width + n_out) * 4;
+  if (smem > 200 * 1024) return LLM_ERR_UNSUPPORTED;
+  if (dtype == LLM_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl(moe_router_kernel<float>, rows, 256, smem, stream, (const float*)h, w, b, z_out, z_stride, width,
+                      E, n_out, top, ids, wts);
+  }
+  if (dtype == LLM_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl(moe_router_kernel<bf16>, rows, 256, smem, stream, (const bf16*)h, w, b, z_out, z_stride, width, E,
+                      n_out, top, ids, wts);
+  }
+  return LLM_ERR_UNSUPPORTED;
 }
 
 LLM_EXPORT int llm_moe_route(const float* z, int z_stride, int rows, int E, int top, int* ids, float* wts,

@@ -94,6 +94,105 @@ __global__ void __launch_bounds__(256) stream_step_kernel(const StreamArgs p, TO
   }
 }
 
+// The same with 16-byte accesses (the width a multiple of four, every base aligned): a thread
+// owns four neighbouring columns at a time, so that a row of a few thousand columns is one access
+// per thread and stream; a step of few rows is then one round trip to memory, not sixteen.
+constexpr int KEEP4 = 4;
+template <typename TOut, int S>
+__global__ void __launch_bounds__(1024) stream_step_vec_kernel(const StreamArgs p, TOut* __restrict__ out) {
+  __shared__ float scratch[33];
+  __shared__ float coef[MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS];
+  pdl_trigger();
+  if (threadIdx.x < S * S) coef[threadIdx.x] = p.y ? p.mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < S) {
+    coef[S * S + threadIdx.x] = p.y ? p.b[threadIdx.x] : 0.f;
+    coef[S * S + S + threadIdx.x] = p.a ? p.a[threadIdx.x] : 0.f;
+  }
+  pdl_wait();
+  __syncthreads();
+  const int r = blockIdx.x, n4 = p.width >> 2;
+  const size_t row = p.rows_index ? (size_t)p.rows_index[r] : (size_t)r;
+  float* x0 = p.xs + row * p.width;
+  float* yr = p.y ? p.y + row * p.width : nullptr;
+  float4 u_keep[KEEP4];
+  float ss = 0.f;
+  auto column = [&](int c) {            // c: first of four columns
+    float v[S][4];
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const float4 t = *reinterpret_cast<const float4*>(x0 + (size_t)s * p.stream_stride + c);
+      v[s][0] = t.x, v[s][1] = t.y, v[s][2] = t.z, v[s][3] = t.w;
+    }
+    if (yr) {
+      const float4 yv4 = *reinterpret_cast<const float4*>(yr + c);
+      const float yv[4] = {yv4.x, yv4.y, yv4.z, yv4.w};
+      if (p.clear_y) *reinterpret_cast<float4*>(yr + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+      float n[S][4];
+#pragma unroll
+      for (int t = 0; t < S; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float acc = 0.f;
+#pragma unroll
+          for (int s = 0; s < S; ++s) acc = fmaf(coef[s * S + t], v[s][e], acc);
+          n[t][e] = fmaf(coef[S * S + t], yv[e], acc);
+        }
+#pragma unroll
+      for (int t = 0; t < S; ++t) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[t][e] = n[t][e];
+        if (p.store)
+          *reinterpret_cast<float4*>(x0 + (size_t)t * p.stream_stride + c) = make_float4(n[t][0], n[t][1], n[t][2], n[t][3]);
+      }
+    }
+    float u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < S; ++s)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) u[e] = fmaf(coef[S * S + S + s], v[s][e], u[e]);
+    return make_float4(u[0], u[1], u[2], u[3]);
+  };
+  auto square = [&](const float4& u) {
+    ss = fmaf(u.x, u.x, ss), ss = fmaf(u.y, u.y, ss), ss = fmaf(u.z, u.z, ss), ss = fmaf(u.w, u.w, ss);
+  };
+#pragma unroll
+  for (int n = 0; n < KEEP4; ++n) {
+    const int c4 = threadIdx.x + n * blockDim.x;
+    if (c4 < n4) {
+      u_keep[n] = column(4 * c4);
+      square(u_keep[n]);
+    }
+  }
+  for (int c4 = threadIdx.x + KEEP4 * blockDim.x; c4 < n4; c4 += blockDim.x) square(column(4 * c4));
+  if (!p.a) return;
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)p.width + p.eps);
+  auto write = [&](int c, const float4& u) {
+    const float4 w = *reinterpret_cast<const float4*>(p.w + c);
+    TOut* dst = out + (size_t)r * p.width + c;
+    dst[0] = from_f32<TOut>(u.x * scale * w.x), dst[1] = from_f32<TOut>(u.y * scale * w.y);
+    dst[2] = from_f32<TOut>(u.z * scale * w.z), dst[3] = from_f32<TOut>(u.w * scale * w.w);
+  };
+#pragma unroll
+  for (int n = 0; n < KEEP4; ++n) {
+    const int c4 = threadIdx.x + n * blockDim.x;
+    if (c4 < n4) write(4 * c4, u_keep[n]);
+  }
+  // beyond what is kept: read again what this thread wrote (a launch that does not store stays
+  // within what is kept)
+  for (int c4 = threadIdx.x + KEEP4 * blockDim.x; c4 < n4; c4 += blockDim.x) {
+    const int c = 4 * c4;
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const float4 t = *reinterpret_cast<const float4*>(x0 + (size_t)s * p.stream_stride + c);
+      const float cs = coef[S * S + S + s];
+      a[0] = fmaf(cs, t.x, a[0]), a[1] = fmaf(cs, t.y, a[1]), a[2] = fmaf(cs, t.z, a[2]), a[3] = fmaf(cs, t.w, a[3]);
+    }
+    write(c, make_float4(a[0], a[1], a[2], a[3]));
+  }
+}
+
 // xs[s][r][:] = xs[0][r][:] for s >= 1: every stream starts as the embedding output
 __global__ void stream_fill_kernel(float* __restrict__ xs, long long stream_stride, long long total, int S) {
   pdl_trigger();
@@ -107,6 +206,20 @@ __global__ void stream_fill_kernel(float* __restrict__ xs, long long stream_stri
 
 template <typename TOut>
 int launch_step(const StreamArgs& p, void* out, int rows, cudaStream_t stream) {
+  const bool vec = (p.width & 3) == 0 && (p.stream_stride & 3) == 0 &&
+                   (((uintptr_t)p.xs | (uintptr_t)p.y | (uintptr_t)p.w) & 15) == 0;
+  if (vec) {
+    int threads = ((p.width >> 2) + 31) & ~31;
+    threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
+    if (p.y == nullptr || p.store || p.width <= 4 * KEEP4 * threads) {
+#define STEPV(N) \
+  case N: return launched_many_blocks(launch_pdl(stream_step_vec_kernel<TOut, N>, rows, threads, 0, stream, p, (TOut*)out), rows)
+      switch (p.S) {
+        STEPV(1); STEPV(2); STEPV(3); STEPV(4); STEPV(5); STEPV(6); STEPV(7); STEPV(8);
+      }
+#undef STEPV
+    }
+  }
   const int threads = p.width >= 1024 ? 256 : 128;
 #define STEP(N) \
   case N: return launched_many_blocks(launch_pdl(stream_step_kernel<TOut, N>, rows, threads, 0, stream, p, (TOut*)out), rows)

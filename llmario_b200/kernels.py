@@ -89,6 +89,7 @@ def _signatures():
         "llm_latent_query": [P, I, P, I, P, P, I, I, I, I, I, I, P],
         "llm_gemm_simt_batched": [P, P, P, I, I, I, I, I, I, I, I, I, L, L, L, P],
         "llm_moe_route": [P, I, I, I, I, P, P, P],
+        "llm_moe_router": [P, I, P, P, P, I, I, I, I, I, I, P, P, P],
         "llm_moe_align": [P, I, I, I, I, P, P, P],
         "llm_moe_gather": [P, P, P, I, I, I, I, P],
         "llm_moe_combine": [P, P, P, P, P, I, P, I, I, I, I, P],
@@ -1165,6 +1166,24 @@ def moe_route(z: torch.Tensor, experts: int, top: int, ids: torch.Tensor, wts: t
     assert wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == (rows, top)
     _check(lib().llm_moe_route(_ptr(z), z.stride(0), rows, experts, top, _ptr(ids), _ptr(wts),
                                _stream()), "moe_route")
+
+
+def moe_router(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], experts: int,
+               top: int, z: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor) -> None:
+    """Router logits ``z = h w^T + bias`` (w float32 [n_out, width], sums in 32-bit) and, over
+    the first ``experts`` of them, the ``top`` largest per row into ``ids`` with the softmax over
+    the chosen into ``wts``: the product and :func:`moe_route` in one launch."""
+    _cuda(h, w, bias, z, ids, wts)
+    rows, width = h.shape
+    n_out = w.shape[0]
+    assert w.dtype == torch.float32 and w.is_contiguous() and w.shape[1] == width
+    assert h.is_contiguous() and z.dtype == torch.float32 and z.shape == (rows, n_out)
+    assert z.stride(1) == 1 and (bias is None or (bias.dtype == torch.float32 and bias.numel() == n_out))
+    assert ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (rows, top)
+    assert wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == (rows, top)
+    _check(lib().llm_moe_router(_ptr(h), _dt(h), _ptr(w), _ptr(bias), _ptr(z), z.stride(0), rows,
+                                width, experts, n_out, top, _ptr(ids), _ptr(wts), _stream()),
+           "moe_router")
 
 
 def moe_gate_up_rows(h: torch.Tensor, gate_up: torch.Tensor, ids: torch.Tensor,

@@ -155,10 +155,13 @@ class RoutedExperts:
                 accumulate: bool = True) -> None:
         rows, E, top = ctx.rows, self.experts, self.top
         z = ctx.buffer("moe.logits", (rows, self.router.out_features), torch.float32)
-        self.router(h, z)
         ids = ctx.buffer("moe.ids", (rows, top), torch.int32)
         wts = ctx.buffer("moe.weights", (rows, top), torch.float32)
-        kernels.moe_route(z, E, top, ids, wts)
+        if (self.hidden + self.router.out_features) * 4 <= 200 * 1024:
+            kernels.moe_router(h, self.router.weight, self.router.bias, E, top, z, ids, wts)
+        else:           # a row too wide to stage: the product, then the choice
+            self.router(h, z)
+            kernels.moe_route(z, E, top, ids, wts)
         shared = gate = None
         if self.shared is not None:
             shared = ctx.buffer("moe.shared", (rows, self.hidden), torch.float32)

@@ -189,6 +189,21 @@ def test_route_kernel(E, top):
         assert ids[r].cpu().tolist() == chosen.tolist(), r
         w = np.exp(zf[r][chosen] - zf[r][chosen].max())
         np.testing.assert_allclose(wts[r].cpu().numpy(), w / w.sum(), rtol=1e-5)
+    # the product and the choice in one launch: logits of 32-bit weights, one row more than experts
+    for dtype, width in ((torch.float32, 50), (torch.bfloat16, 256)):
+        h = torch.tensor(rng.standard_normal((rows, width)), dtype=dtype, device="cuda")
+        w = torch.tensor(rng.standard_normal((E + 1, width)), dtype=torch.float32, device="cuda")
+        b = torch.tensor(rng.standard_normal(E + 1), dtype=torch.float32, device="cuda")
+        z2 = torch.empty(rows, E + 1, dtype=torch.float32, device="cuda")
+        kernels.moe_router(h, w, b, E, top, z2, ids, wts)
+        ref = h.double().cpu().numpy() @ w.double().cpu().numpy().T + b.double().cpu().numpy()
+        np.testing.assert_allclose(z2.cpu().numpy(), ref, rtol=1e-4, atol=1e-4)
+        zf = z2[:, :E].cpu().numpy().astype(np.float64)
+        for r in range(rows):
+            chosen = np.argsort(-zf[r], kind="stable")[:top]
+            assert ids[r].cpu().tolist() == chosen.tolist(), r
+            w_ = np.exp(zf[r][chosen] - zf[r][chosen].max())
+            np.testing.assert_allclose(wts[r].cpu().numpy(), w_ / w_.sum(), rtol=1e-5)
 
 
 @pytest.mark.gpu
