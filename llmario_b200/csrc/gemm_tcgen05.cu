@@ -59,7 +59,12 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     const __grid_constant__ CUtensorMap map_c, int tma_out, TC* __restrict__ C, int ldc, int T, int N,
     int K, int half, int interleaved, int* __restrict__ status, const int* __restrict__ tile_group,
-    int group_rows) {
+    int group_rows, int batch_x_cols, int batch_c_cols) {
+  // Batched form (batch_x_cols > 0): blockIdx.z is one of several independent products (a head
+  // of a per-head map) instead of a part of K: product z reads the columns z * batch_x_cols .. of
+  // X and the matrix z of W (group_rows rows each) and writes the columns z * batch_c_cols .. of C.
+  // Its last block of K may reach into the next product's columns of X: W's columns end at K,
+  // so what is read there meets zeros.
   extern __shared__ uint8_t raw[];
   auto& sm = *reinterpret_cast<SharedStorage<BN, STAGES>*>(
       (reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -69,8 +74,12 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
   const int n0 = blockIdx.x * feat_per_tile;
   const int t0 = blockIdx.y * BN;
   const int kblocks = (K + TILE_K - 1) / TILE_K;
-  const int per_split = (kblocks + gridDim.z - 1) / gridDim.z;
-  const int kb_begin = blockIdx.z * per_split;
+  const bool batched = batch_x_cols > 0;
+  const int n_splits = batched ? 1 : (int)gridDim.z, split_idx = batched ? 0 : (int)blockIdx.z;
+  const int per_split = (kblocks + n_splits - 1) / n_splits;
+  const int kb_begin = split_idx * per_split;
+  const int x_col0 = batched ? (int)blockIdx.z * batch_x_cols : 0;
+  const int c_col0 = batched ? (int)blockIdx.z * batch_c_cols : 0;
   const int kb_end = min(kblocks, kb_begin + per_split);
   const int nkb = kb_end - kb_begin;
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
@@ -95,7 +104,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  int w_row0 = 0;          // first row of this tile's matrix inside W
+  int w_row0 = batched ? (int)blockIdx.z * group_rows : 0;          // first row of this tile's matrix inside W
   bool live = nkb > 0;
   if (tile_group) {
     pdl_wait();
@@ -129,7 +138,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
       };
       auto load_x = [&](int i) {
         const int s = i % STAGES;
-        tma_load_2d(sm.b[s], &map_x, (kb_begin + i) * TILE_K, t0, &sm.full[s]);
+        tma_load_2d(sm.b[s], &map_x, x_col0 + (kb_begin + i) * TILE_K, t0, &sm.full[s]);
       };
       const int head = min(nkb, STAGES);
       for (int i = 0; i < head; ++i) load_w(i);
@@ -177,7 +186,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
       if (!ok && lane == 0) atomicExch(status, 3);
       tc_fence_after();
       if (ok) {
-        const bool split = gridDim.z > 1;
+        const bool split = n_splits > 1;
         // With a tensor map for the output the tile is laid out in shared memory as
         // [token][feature] (the pipeline stages are free by now) and written by one TMA store,
         // or added by one TMA reduction (residual add, partial sums of a K split).
@@ -212,7 +221,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
               if (tma_out) {
                 stage_out[(c + j) * FEAT + row] = from_f32<TC>(a);
               } else if (t < T && n < N) {
-                TC* dst = C + (size_t)t * ldc + n;
+                TC* dst = C + (size_t)t * ldc + c_col0 + n;
                 if (EPI == EPI_ACCUM || split) {
                   if (split) atomicAdd(reinterpret_cast<float*>(dst), a);
                   else *dst = from_f32<TC>(to_f32(*dst) + a);
@@ -230,10 +239,10 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
             const uint32_t src = smem_u32(stage_out);
             if (EPI == EPI_ACCUM || split)
               asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
-                           ::"l"(&map_c), "r"(src), "r"(n0), "r"(t0) : "memory");
+                           ::"l"(&map_c), "r"(src), "r"(c_col0 + n0), "r"(t0) : "memory");
             else
               asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                           ::"l"(&map_c), "r"(src), "r"(n0), "r"(t0) : "memory");
+                           ::"l"(&map_c), "r"(src), "r"(c_col0 + n0), "r"(t0) : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           }
@@ -379,12 +388,15 @@ namespace {
 template <int BN, int STAGES, int EPI, typename TC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K, int half,
            int splits, int interleaved, int* status, cudaStream_t stream, const int* tile_group = nullptr,
-           int group_rows = 0) {
+           int group_rows = 0, int batch = 0, int batch_x_cols = 0, int batch_c_cols = 0) {
   // the output goes through TMA when its rows are 16-byte multiples on a 16-byte aligned base
+  // (batched: only when a product's columns are whole tiles, since a tile's store is clipped at
+  // the matrix's edge alone, and its columns start on a 16-byte boundary)
   CUtensorMap mc = mw;
   int tma_out = 0;
-  const int out_cols = EPI == EPI_GATED ? half : N;
-  if (((uintptr_t)C & 15) == 0 && ((size_t)ldc * sizeof(TC)) % 16 == 0 &&
+  const int out_cols = batch ? (batch - 1) * batch_c_cols + N : (EPI == EPI_GATED ? half : N);
+  const bool tiles_fit = !batch || (N % TILE_M == 0 && ((size_t)batch_c_cols * sizeof(TC)) % 16 == 0);
+  if (tiles_fit && ((uintptr_t)C & 15) == 0 && ((size_t)ldc * sizeof(TC)) % 16 == 0 &&
       llm_tensor_map(C, T, out_cols, ldc, BN, EPI == EPI_GATED ? 64 : TILE_M, sizeof(TC) == 4 ? 2 : 1, &mc))
     tma_out = 1;
   auto kernel = gemm_tcgen05_kernel<BN, STAGES, EPI, TC>;
@@ -397,20 +409,20 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, 
   }
   const int feat = EPI == EPI_GATED ? 64 : TILE_M;
   const int limit = EPI == EPI_GATED ? half : N;
-  dim3 grid((limit + feat - 1) / feat, (T + BN - 1) / BN, splits);
+  dim3 grid((limit + feat - 1) / feat, (T + BN - 1) / BN, batch ? batch : splits);
   return launch_pdl(kernel, grid, 192, smem, stream, mw, mx, mc, tma_out, C, ldc, T, N, K, half, interleaved,
-                    status, tile_group, group_rows);
+                    status, tile_group, group_rows, batch_x_cols, batch_c_cols);
 }
 
 template <int EPI, typename TC>
 int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K,
              int half, int splits, int interleaved, int* status, cudaStream_t stream,
-             const int* tile_group = nullptr, int group_rows = 0) {
+             const int* tile_group = nullptr, int group_rows = 0, int batch = 0, int bx = 0, int bc = 0) {
   switch (bn) {
-    case 16: return launch<16, 6, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows);
-    case 32: return launch<32, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows);
-    case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows);
-    case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows);
+    case 16: return launch<16, 6, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows, batch, bx, bc);
+    case 32: return launch<32, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows, batch, bx, bc);
+    case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows, batch, bx, bc);
+    case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream, tile_group, group_rows, batch, bx, bc);
   }
   return LLM_ERR_UNSUPPORTED;
 }
@@ -509,5 +521,28 @@ LLM_EXPORT int llm_gemm_tcgen05_grouped(const void* X, const void* W, void* C, i
     return dispatch<EPI_GATED, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, half, 1, 0, status, stream, tile_group, N);
   if (c_dtype == LLM_F32)
     return dispatch<EPI_GATED, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, 1, 0, status, stream, tile_group, N);
+  return LLM_ERR_UNSUPPORTED;
+}
+
+// The batched product: `batch` independent products C_z = X_z W_z^T in one launch.  X_z is the
+// columns z * x_cols .. z * x_cols + K of X [T][>= (batch - 1) * x_cols + K] (row stride lda),
+// W_z the rows z * N .. of W [batch * N][K], C_z the columns z * c_cols .. z * c_cols + N of C
+// (row stride ldc; bf16 or f32).  x_cols a multiple of 8.  No split of K (a head's K is short).
+LLM_EXPORT int llm_gemm_tcgen05_batched(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
+                                        int lda, int ldw, int ldc, int bn, int batch, int x_cols, int c_cols,
+                                        int* status, cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || x_cols % 8 || x_cols <= 0 || c_cols < N) return LLM_ERR_UNSUPPORTED;
+  if (((uintptr_t)X | (uintptr_t)W) & 15) return LLM_ERR_UNSUPPORTED;
+  if (batch > 65535 || (long long)batch * N > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
+  CUtensorMap mw, mx;
+  if (!llm_tensor_map(W, (long long)batch * N, K, ldw, TILE_M, TILE_K, 0, &mw)) return LLM_ERR_UNSUPPORTED;
+  if (!llm_tensor_map(X, T, (long long)(batch - 1) * x_cols + K, lda, bn, TILE_K, 0, &mx)) return LLM_ERR_UNSUPPORTED;
+  if (c_dtype == LLM_F32)
+    return dispatch<EPI_STORE, float>(bn, mw, mx, (float*)C, ldc, T, N, K, 0, 1, 0, status, stream, nullptr, N, batch,
+                                      x_cols, c_cols);
+  if (c_dtype == LLM_BF16)
+    return dispatch<EPI_STORE, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, 0, 1, 0, status, stream, nullptr, N, batch,
+                                     x_cols, c_cols);
   return LLM_ERR_UNSUPPORTED;
 }

@@ -94,6 +94,7 @@ def _signatures():
         "llm_moe_gather": [P, P, P, I, I, I, I, P],
         "llm_moe_combine": [P, P, P, P, P, I, P, I, I, I, I, P],
         "llm_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, P],
+        "llm_gemm_tcgen05_batched": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "llm_moe_gate_up_rows": [P, P, P, P, I, I, I, I, I, P],
         "llm_moe_down_rows": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, P],
         "llm_causal_conv_silu": [P, I, P, P, P, L, P, P, I, I, I, P, I, I, I, P],
@@ -1144,11 +1145,15 @@ def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     n = w.shape[1]
     assert w.shape == (H, n, k) and w.is_contiguous() and out.shape == (rows, H, n)
     assert a.stride(2) == 1 and out.stride(2) == 1 and a.dtype == w.dtype
-    if rows > HEAD_LINEAR_SIMT_ROWS and all(_tc_ok(a[:, h], w[h], out[:, h]) for h in range(H)):
-        # (the one-CTA kernel also for many rows: a head's product is small, and CTA-pair
-        # products are never launched one directly behind the other)
-        for h in range(H):
-            gemm_tcgen05(a[:, h], w[h], out[:, h], 0, bn=128)
+    if (rows > HEAD_LINEAR_SIMT_ROWS and a.dtype == torch.bfloat16 and k % 8 == 0
+            and a.stride(0) % 8 == 0 and a.stride(1) % 8 == 0 and a.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and out.stride(1) >= n):
+        # every head's product in one launch of the tensor-core kernel (its one-CTA form:
+        # a head's product is small)
+        _check(lib().llm_gemm_tcgen05_batched(_ptr(a), _ptr(w), _ptr(out), _dt(out), rows, n, k,
+                                              a.stride(0), k, out.stride(0), 128, H, a.stride(1),
+                                              out.stride(1), _ptr(tc_status(a.device)),
+                                              _stream()), "head_linear")
         return
     _check(lib().llm_gemm_simt_batched(_ptr(a), _ptr(w), _ptr(out), _dt(a), _dt(out), rows, n, k,
                                        a.stride(0), k, out.stride(0), H, a.stride(1), n * k,

@@ -212,7 +212,8 @@ def test_head_linear_and_gated_activation(dtype):
     from llmario_b200 import kernels
 
     rng = np.random.default_rng(3)
-    for rows, H, k, n in ((5, 3, 10, 7), (70, 4, 32, 96), (300, 2, 96, 48)):
+    for rows, H, k, n in ((5, 3, 10, 7), (70, 4, 32, 96), (300, 2, 96, 48), (300, 3, 64, 128),
+                          (1000, 16, 96, 96), (200, 5, 24, 256)):
         a = torch.tensor(rng.standard_normal((rows, H, k + 8)), dtype=dtype, device="cuda")
         w = torch.tensor(rng.standard_normal((H, n, k)), dtype=dtype, device="cuda")
         out = torch.zeros(rows, H, n + 8, dtype=dtype, device="cuda")
