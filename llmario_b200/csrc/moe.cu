@@ -59,44 +59,65 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 }
 
 
-// Router logits and the choice in one kernel, one block per row: the row of h is staged in shared
-// memory in 32-bit, every warp makes logits z[e] = w[e] . h + b[e] (w and b 32-bit, sums in a
-// fixed order), then warp 0 chooses as moe_route_kernel does.  Rows of w behind the E experts'
+// Router logits and the choice in one kernel.  A block takes R rows: their h is staged in shared
+// memory in 32-bit, every warp makes, for its experts, the logits z[e] = w[e] . h + b[e] of all R
+// rows from one reading of w[e] (w and b 32-bit, sums in a fixed order that does not depend on
+// R), then warp i chooses for row i as moe_route_kernel does.  Rows of w behind the E experts'
 // (n_out - E of them: the gate of a shared expert) get their logits too; all go to z_out.
-template <typename T>
+template <typename T, int R>
 __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h, const float* __restrict__ w,
                                                          const float* __restrict__ b, float* __restrict__ z_out,
-                                                         int z_stride, int width, int E, int n_out, int top,
-                                                         int* __restrict__ ids, float* __restrict__ wts) {
-  extern __shared__ float rs[];        // h[width], z[n_out]
+                                                         int z_stride, int rows, int width, int E, int n_out,
+                                                         int top, int* __restrict__ ids, float* __restrict__ wts) {
+  extern __shared__ float rs[];        // h[R][width], z[R][n_out]
   float* h_s = rs;
-  float* z_s = rs + width;
+  float* z_s = rs + (size_t)R * width;
   pdl_trigger();
   pdl_wait();
-  const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) h_s[i] = to_f32(h[(size_t)r * width + i]);
+  const int r0 = blockIdx.x * R, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < R * width; i += blockDim.x) {
+    const int rr = i / width, c = i - rr * width;
+    h_s[i] = r0 + rr < rows ? to_f32(h[(size_t)(r0 + rr) * width + c]) : 0.f;
+  }
   __syncthreads();
+  const bool wide = (width & 3) == 0 && ((uintptr_t)w & 15) == 0;
   for (int e = warp; e < n_out; e += nwarps) {
     const float* we = w + (size_t)e * width;
-    float acc = 0.f;
-    if ((width & 3) == 0 && ((uintptr_t)we & 15) == 0) {
+    float acc[R];
+#pragma unroll
+    for (int rr = 0; rr < R; ++rr) acc[rr] = 0.f;
+    if (wide) {
+#pragma unroll 4
       for (int i = lane * 4; i < width; i += 128) {
         const float4 a = *reinterpret_cast<const float4*>(we + i);
-        acc = fmaf(a.x, h_s[i], acc), acc = fmaf(a.y, h_s[i + 1], acc);
-        acc = fmaf(a.z, h_s[i + 2], acc), acc = fmaf(a.w, h_s[i + 3], acc);
+#pragma unroll
+        for (int rr = 0; rr < R; ++rr) {
+          const float* hr = h_s + (size_t)rr * width + i;
+          acc[rr] = fmaf(a.x, hr[0], acc[rr]), acc[rr] = fmaf(a.y, hr[1], acc[rr]);
+          acc[rr] = fmaf(a.z, hr[2], acc[rr]), acc[rr] = fmaf(a.w, hr[3], acc[rr]);
+        }
       }
     } else {
-      for (int i = lane; i < width; i += 32) acc = fmaf(we[i], h_s[i], acc);
+      for (int i = lane; i < width; i += 32) {
+        const float a = we[i];
+#pragma unroll
+        for (int rr = 0; rr < R; ++rr) acc[rr] = fmaf(a, h_s[(size_t)rr * width + i], acc[rr]);
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      const float v = acc + (b ? b[e] : 0.f);
-      z_s[e] = v;
-      z_out[(size_t)r * z_stride + e] = v;
+#pragma unroll
+    for (int rr = 0; rr < R; ++rr) {
+      const float sum = warp_sum(acc[rr]);
+      if (lane == 0 && r0 + rr < rows) {
+        const float v = sum + (b ? b[e] : 0.f);
+        z_s[rr * n_out + e] = v;
+        z_out[(size_t)(r0 + rr) * z_stride + e] = v;
+      }
     }
   }
   __syncthreads();
-  if (warp != 0) return;
+  if (warp >= R || r0 + warp >= rows) return;
+  const int r = r0 + warp;
+  const float* zr = z_s + warp * n_out;
   float best[MAX_TOP];
   int pick[MAX_TOP];
   for (int k = 0; k < top; ++k) {
@@ -105,7 +126,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h
     for (int e = lane; e < E; e += 32) {
       bool taken = false;
       for (int j = 0; j < k; ++j) taken |= pick[j] == e;
-      const float x = z_s[e];
+      const float x = zr[e];
       if (!taken && (x > v || (x == v && e < at) || at == 0x7fffffff)) v = x, at = e;
     }
 #pragma unroll
@@ -311,20 +332,28 @@ LLM_EXPORT int llm_moe_router(const void* h, int dtype, const float* w, const fl
                               cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (top < 1 || top > MAX_TOP || top > E || n_out < E) return LLM_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)(width + n_out) * 4;
-  if (smem > 200 * 1024) return LLM_ERR_UNSUPPORTED;
+  if ((size_t)(width + n_out) * 4 > 200 * 1024) return LLM_ERR_UNSUPPORTED;
+  // many rows: four to a block, so that a block reads the router's rows once for four tokens
+  const bool four = rows >= 256 && (size_t)4 * (width + n_out) * 4 <= 200 * 1024;
+  const int R = four ? 4 : 1;
+  const size_t smem = (size_t)R * (width + n_out) * 4;
+  const int blocks = (rows + R - 1) / R;
+#define ROUTER(T, RR)                                                                                          \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      cudaFuncSetAttribute(moe_router_kernel<T, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    return launch_pdl(moe_router_kernel<T, RR>, blocks, 256, smem, stream, (const T*)h, w, b, z_out, z_stride, \
+                      rows, width, E, n_out, top, ids, wts);                                                   \
+  } while (0)
   if (dtype == LLM_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_pdl(moe_router_kernel<float>, rows, 256, smem, stream, (const float*)h, w, b, z_out, z_stride, width,
-                      E, n_out, top, ids, wts);
+    if (four) ROUTER(float, 4);
+    ROUTER(float, 1);
   }
   if (dtype == LLM_BF16) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_pdl(moe_router_kernel<bf16>, rows, 256, smem, stream, (const bf16*)h, w, b, z_out, z_stride, width, E,
-                      n_out, top, ids, wts);
+    if (four) ROUTER(bf16, 4);
+    ROUTER(bf16, 1);
   }
+#undef ROUTER
   return LLM_ERR_UNSUPPORTED;
 }
 
