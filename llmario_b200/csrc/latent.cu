@@ -15,26 +15,33 @@ namespace {
 // is normed (gain wc) into the row's place in the K plane and, the same values, the V plane;
 // the key part is rotated by the row's angles (cos_sin[row][i] = (cos, sin) of angle i, the first
 // rot_half pairs; null: no rotation) and written behind the latent in the K plane.  The V plane's
-// channels behind the latent are never written and stay zero.
+// channels behind the latent are never written and stay zero.  clear_proj: the row of proj that
+// was read is zeroed at the end (it lies in a buffer that a split-K product adds into).
 template <typename T>
 __global__ void __launch_bounds__(128) latent_store_kernel(
-    const float* __restrict__ proj, int proj_stride, const float* __restrict__ wq, const float* __restrict__ wc,
+    float* __restrict__ proj, int proj_stride, const float* __restrict__ wq, const float* __restrict__ wc,
     const float2* __restrict__ cos_sin, int rot_half, T* __restrict__ cq_out, T* __restrict__ k_plane,
     T* __restrict__ v_plane, long long page_stride, const int* __restrict__ block_table, int table_stride,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, int page_size, int q_rank, int kv_rank,
-    int rot_dim, float eps, int write_cache) {
+    int rot_dim, float eps, int write_cache, int clear_proj) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x, tid = threadIdx.x;
-  const float* p = proj + (size_t)r * proj_stride;
+  float* p = proj + (size_t)r * proj_stride;
   float ss = 0.f;
   for (int i = tid; i < q_rank; i += blockDim.x) ss = fmaf(p[i], p[i], ss);
   ss = block_sum(ss, scratch);
   const float sq = 1.0f / sqrtf(ss / (float)q_rank + eps);
   for (int i = tid; i < q_rank; i += blockDim.x)
     cq_out[(size_t)r * q_rank + i] = from_f32<T>(p[i] * sq * wq[i]);
-  if (!write_cache) return;
+  if (!write_cache) {
+    if (clear_proj) {
+      __syncthreads();
+      for (int i = tid; i < q_rank + kv_rank + rot_dim; i += blockDim.x) p[i] = 0.f;
+    }
+    return;
+  }
   const float* c = p + q_rank;
   ss = 0.f;
   for (int i = tid; i < kv_rank; i += blockDim.x) ss = fmaf(c[i], c[i], ss);
@@ -60,15 +67,21 @@ __global__ void __launch_bounds__(128) latent_store_kernel(
     }
     k_plane[off + kv_rank + j] = from_f32<T>(v);
   }
+  if (clear_proj) {
+    __syncthreads();
+    for (int i = tid; i < q_rank + kv_rank + rot_dim; i += blockDim.x) p[i] = 0.f;
+  }
 }
 
 // q[row][h] = [ plain part (dim) | part to rotate (rot_dim) ] in 32-bit.  The plain part is rounded
 // into q_plain[row][h][0:dim] (the operand of the product with U_k,h); the rotated part goes to
-// q_full[row][h][kv_rank : kv_rank + rot_dim], behind the place of that product's result.
+// q_full[row][h][kv_rank : kv_rank + rot_dim], behind the place of that product's result.  A pair
+// of the rotated part is one thread's work (both values read, both written).  clear: what was
+// read of q is zeroed.
 template <typename T>
-__global__ void latent_query_kernel(const float* __restrict__ q, int q_stride, const float2* __restrict__ cos_sin,
+__global__ void latent_query_kernel(float* __restrict__ q, int q_stride, const float2* __restrict__ cos_sin,
                                     int rot_half, T* __restrict__ q_plain, T* __restrict__ q_full, long long total,
-                                    int H, int dim, int rot_dim, int kv_rank) {
+                                    int H, int dim, int rot_dim, int kv_rank, int clear) {
   pdl_trigger();
   pdl_wait();
   const int per_head = dim + rot_dim, hd = kv_rank + rot_dim;
@@ -78,46 +91,57 @@ __global__ void latent_query_kernel(const float* __restrict__ q, int q_stride, c
     const int e = (int)(idx - rh * per_head);
     const long long r = rh / H;
     const int h = (int)(rh - r * H);
-    const float* src = q + (size_t)r * q_stride + (size_t)h * per_head;
+    float* src = q + (size_t)r * q_stride + (size_t)h * per_head;
     if (e < dim) {
       q_plain[(size_t)rh * dim + e] = from_f32<T>(src[e]);
+      if (clear) src[e] = 0.f;
     } else {
       const int j = e - dim, i = j >> 1;
-      float v = src[e];
+      if (j & 1) continue;                       // the pair's even member does both
+      const bool two = j + 1 < rot_dim;
+      const float a = src[e], b = two ? src[e + 1] : 0.f;
+      float va = a, vb = b;
       if (cos_sin && i < rot_half) {
         const float2 cs = cos_sin[(size_t)r * rot_half + i];
-        const float a = src[dim + 2 * i], b = src[dim + 2 * i + 1];
-        v = (j & 1) ? fmaf(b, cs.x, a * cs.y) : fmaf(a, cs.x, -b * cs.y);
+        va = fmaf(a, cs.x, -b * cs.y);
+        vb = fmaf(b, cs.x, a * cs.y);
       }
-      q_full[(size_t)rh * hd + kv_rank + j] = from_f32<T>(v);
+      T* dst = q_full + (size_t)rh * hd + kv_rank + j;
+      dst[0] = from_f32<T>(va);
+      if (two) dst[1] = from_f32<T>(vb);
+      if (clear) {
+        src[e] = 0.f;
+        if (two) src[e + 1] = 0.f;
+      }
     }
   }
 }
 }  // namespace
 
-LLM_EXPORT int llm_latent_store(const float* proj, int proj_stride, const float* wq, const float* wc,
+LLM_EXPORT int llm_latent_store(float* proj, int proj_stride, const float* wq, const float* wc,
                                 const float* cos_sin, int rot_half, void* cq_out, void* k_plane, void* v_plane,
                                 int dtype, long long page_stride, const int* block_table, int table_stride,
                                 const int* row_slot, const int* row_pos, int rows, int page_size, int q_rank,
-                                int kv_rank, int rot_dim, float eps, int write_cache, cudaStream_t stream) {
+                                int kv_rank, int rot_dim, float eps, int write_cache, int clear_proj,
+                                cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (q_rank <= 0 || kv_rank <= 0 || rot_dim < 0 || 2 * rot_half > rot_dim) return LLM_ERR_ARGUMENT;
   if (dtype == LLM_F32)
     return launched_many_blocks(launch_pdl(latent_store_kernel<float>, rows, 128, 0, stream, proj, proj_stride, wq, wc,
                       (const float2*)cos_sin, rot_half, (float*)cq_out, (float*)k_plane, (float*)v_plane,
                       page_stride, block_table, table_stride, row_slot, row_pos, page_size, q_rank, kv_rank,
-                      rot_dim, eps, write_cache), rows);
+                      rot_dim, eps, write_cache, clear_proj), rows);
   if (dtype == LLM_BF16)
     return launched_many_blocks(launch_pdl(latent_store_kernel<bf16>, rows, 128, 0, stream, proj, proj_stride, wq, wc,
                       (const float2*)cos_sin, rot_half, (bf16*)cq_out, (bf16*)k_plane, (bf16*)v_plane,
                       page_stride, block_table, table_stride, row_slot, row_pos, page_size, q_rank, kv_rank,
-                      rot_dim, eps, write_cache), rows);
+                      rot_dim, eps, write_cache, clear_proj), rows);
   return LLM_ERR_UNSUPPORTED;
 }
 
-LLM_EXPORT int llm_latent_query(const float* q, int q_stride, const float* cos_sin, int rot_half, void* q_plain,
+LLM_EXPORT int llm_latent_query(float* q, int q_stride, const float* cos_sin, int rot_half, void* q_plain,
                                 void* q_full, int dtype, int rows, int H, int dim, int rot_dim, int kv_rank,
-                                cudaStream_t stream) {
+                                int clear, cudaStream_t stream) {
   const long long total = (long long)rows * H * (dim + rot_dim);
   if (total <= 0) return 0;
   if (2 * rot_half > rot_dim) return LLM_ERR_ARGUMENT;
@@ -125,10 +149,10 @@ LLM_EXPORT int llm_latent_query(const float* q, int q_stride, const float* cos_s
   if (dtype == LLM_F32)
     return launched_many_blocks(
         launch_pdl(latent_query_kernel<float>, blocks, 256, 0, stream, q, q_stride, (const float2*)cos_sin, rot_half,
-                   (float*)q_plain, (float*)q_full, total, H, dim, rot_dim, kv_rank), blocks);
+                   (float*)q_plain, (float*)q_full, total, H, dim, rot_dim, kv_rank, clear), blocks);
   if (dtype == LLM_BF16)
     return launched_many_blocks(
         launch_pdl(latent_query_kernel<bf16>, blocks, 256, 0, stream, q, q_stride, (const float2*)cos_sin, rot_half,
-                   (bf16*)q_plain, (bf16*)q_full, total, H, dim, rot_dim, kv_rank), blocks);
+                   (bf16*)q_plain, (bf16*)q_full, total, H, dim, rot_dim, kv_rank, clear), blocks);
   return LLM_ERR_UNSUPPORTED;
 }

@@ -201,9 +201,9 @@ __global__ void __launch_bounds__(128) moe_gate_up_rows_kernel(const T* __restri
 template <typename T>
 __global__ void __launch_bounds__(128) moe_down_rows_kernel(const T* __restrict__ act, const T* __restrict__ down,
                                                             const int* __restrict__ ids, const float* __restrict__ wts,
-                                                            const float* __restrict__ shared, const float* __restrict__ gate,
+                                                            float* __restrict__ shared, const float* __restrict__ gate,
                                                             int gate_stride, float* __restrict__ y, int width, int ff,
-                                                            int top, int accumulate) {
+                                                            int top, int accumulate, int clear_shared) {
   extern __shared__ float a_s[];
   pdl_trigger();
   pdl_wait();
@@ -219,7 +219,10 @@ __global__ void __launch_bounds__(128) moe_down_rows_kernel(const T* __restrict_
       sum = fmaf(wts[(size_t)r * top + k], d, sum);
     }
     if (lane == 0) {
-      if (shared) sum = fmaf(1.f / (1.f + expf(-gate[(size_t)r * gate_stride])), shared[(size_t)r * width + c], sum);
+      if (shared) {
+        sum = fmaf(1.f / (1.f + expf(-gate[(size_t)r * gate_stride])), shared[(size_t)r * width + c], sum);
+        if (clear_shared) shared[(size_t)r * width + c] = 0.f;
+      }
       float* dst = y + (size_t)r * width + c;
       *dst = accumulate ? *dst + sum : sum;
     }
@@ -280,9 +283,10 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const T* __restrict__ h
 // y[r][c] (+)= sum_k wts[r][k] * d[pos[r * top + k]][c]  (+ sigmoid(gate[r]) * shared[r][c]), k ascending
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ d, const int* __restrict__ pos,
                                                           const float* __restrict__ wts,
-                                                          const float* __restrict__ shared,
+                                                          float* __restrict__ shared,
                                                           const float* __restrict__ gate, int gate_stride,
-                                                          float* __restrict__ y, int width, int top, int accumulate) {
+                                                          float* __restrict__ y, int width, int top, int accumulate,
+                                                          int clear_shared) {
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
@@ -291,7 +295,10 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
     float sum = 0.f;
     for (int k = 0; k < top; ++k)
       sum = fmaf(wts[(size_t)r * top + k], d[(size_t)pos[(size_t)r * top + k] * width + c], sum);
-    if (shared) sum = fmaf(g, shared[(size_t)r * width + c], sum);
+    if (shared) {
+      sum = fmaf(g, shared[(size_t)r * width + c], sum);
+      if (clear_shared) shared[(size_t)r * width + c] = 0.f;
+    }
     float* dst = y + (size_t)r * width + c;
     *dst = accumulate ? *dst + sum : sum;
   }
@@ -316,13 +323,13 @@ LLM_EXPORT int llm_moe_gather(const void* h, const int* pos, void* xp, int dtype
   return LLM_ERR_UNSUPPORTED;
 }
 
-LLM_EXPORT int llm_moe_combine(const float* d, const int* pos, const float* wts, const float* shared,
+LLM_EXPORT int llm_moe_combine(const float* d, const int* pos, const float* wts, float* shared,
                                const float* gate, int gate_stride, float* y, int rows, int width, int top,
-                               int accumulate, cudaStream_t stream) {
+                               int accumulate, int clear_shared, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (shared && !gate) return LLM_ERR_ARGUMENT;
   return launched_many_blocks(launch_pdl(moe_combine_kernel, rows, 256, 0, stream, d, pos, wts, shared, gate,
-                                         gate_stride, y, width, top, accumulate), rows);
+                                         gate_stride, y, width, top, accumulate, clear_shared), rows);
 }
 
 // The router: z_out[r][0:n_out] = w h_r + b (w float32 [n_out][width], the first E rows the
@@ -386,8 +393,9 @@ LLM_EXPORT int llm_moe_gate_up_rows(const void* h, const void* gate_up, const in
 }
 
 LLM_EXPORT int llm_moe_down_rows(const void* act, const void* down, const int* ids, const float* wts,
-                                 const float* shared, const float* gate, int gate_stride, float* y, int dtype,
-                                 int rows, int width, int ff, int top, int accumulate, cudaStream_t stream) {
+                                 float* shared, const float* gate, int gate_stride, float* y, int dtype,
+                                 int rows, int width, int ff, int top, int accumulate, int clear_shared,
+                                 cudaStream_t stream) {
   if (rows <= 0) return 0;
   const size_t smem = (size_t)top * ff * 4;
   if ((width + 7) / 8 > 65535 || smem > 200 * 1024) return LLM_ERR_UNSUPPORTED;
@@ -397,13 +405,13 @@ LLM_EXPORT int llm_moe_down_rows(const void* act, const void* down, const int* i
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_down_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_pdl(moe_down_rows_kernel<float>, grid, 128, smem, stream, (const float*)act, (const float*)down,
-                      ids, wts, shared, gate, gate_stride, y, width, ff, top, accumulate);
+                      ids, wts, shared, gate, gate_stride, y, width, ff, top, accumulate, clear_shared);
   }
   if (dtype == LLM_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_down_rows_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_pdl(moe_down_rows_kernel<bf16>, grid, 128, smem, stream, (const bf16*)act, (const bf16*)down, ids,
-                      wts, shared, gate, gate_stride, y, width, ff, top, accumulate);
+                      wts, shared, gate, gate_stride, y, width, ff, top, accumulate, clear_shared);
   }
   return LLM_ERR_UNSUPPORTED;
 }

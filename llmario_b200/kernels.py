@@ -83,20 +83,20 @@ def _signatures():
         "llm_memory_out_norm": [P, I, P, I, P, I, P, P, I, I, I, I, I, F, F, P],
         "llm_stream_step": [P, L, I, P, P, P, I, I, P, P, F, P, I, P, I, I, P],
         "llm_stream_fill": [P, L, I, I, I, P],
-        "llm_gated_act": [P, P, P, I, I, I, I, P],
+        "llm_gated_act": [P, P, P, I, I, I, I, I, P],
         "llm_scale_soft_cap": [P, L, F, F, P],
-        "llm_latent_store": [P, I, P, P, P, I, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P],
-        "llm_latent_query": [P, I, P, I, P, P, I, I, I, I, I, I, P],
+        "llm_latent_store": [P, I, P, P, P, I, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, I, P],
+        "llm_latent_query": [P, I, P, I, P, P, I, I, I, I, I, I, I, P],
         "llm_gemm_simt_batched": [P, P, P, I, I, I, I, I, I, I, I, I, L, L, L, P],
         "llm_moe_route": [P, I, I, I, I, P, P, P],
         "llm_moe_router": [P, I, P, P, P, I, I, I, I, I, I, P, P, P],
         "llm_moe_align": [P, I, I, I, I, P, P, P],
         "llm_moe_gather": [P, P, P, I, I, I, I, P],
-        "llm_moe_combine": [P, P, P, P, P, I, P, I, I, I, I, P],
+        "llm_moe_combine": [P, P, P, P, P, I, P, I, I, I, I, I, P],
         "llm_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, P],
         "llm_gemm_tcgen05_batched": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "llm_moe_gate_up_rows": [P, P, P, P, I, I, I, I, I, P],
-        "llm_moe_down_rows": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, P],
+        "llm_moe_down_rows": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, P],
         "llm_causal_conv_silu": [P, I, P, P, P, L, P, P, I, I, I, P, I, I, I, P],
         "llm_gated_group_norm": [P, I, P, I, P, I, P, I, P, I, P, I, I, I, I, I, F, I, P],
     }
@@ -1077,15 +1077,16 @@ ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
 
 def gated_act(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-              activation: str) -> None:
-    """out[t][j] = act(gate_up[t][j] + bias[j]) * (gate_up[t][ff + j] + bias[ff + j])."""
+              activation: str, clear: bool = False) -> None:
+    """out[t][j] = act(gate_up[t][j] + bias[j]) * (gate_up[t][ff + j] + bias[ff + j]).
+    ``clear``: gate_up is zeroed once read (a buffer that is kept at zero between steps)."""
     _cuda(gate_up, bias, out)
     rows, ff = out.shape
     assert gate_up.dtype == torch.float32 and gate_up.is_contiguous() and out.is_contiguous()
     assert gate_up.shape == (rows, 2 * ff)
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * ff)
     _check(lib().llm_gated_act(_ptr(gate_up), _ptr(bias), _ptr(out), _dt(out), rows, ff,
-                               ACTIVATIONS[activation], _stream()), "gated_act")
+                               ACTIVATIONS[activation], int(clear), _stream()), "gated_act")
 
 
 def scale_soft_cap(z: torch.Tensor, scale: float, cap: float) -> None:
@@ -1099,7 +1100,7 @@ def scale_soft_cap(z: torch.Tensor, scale: float, cap: float) -> None:
 def latent_store(proj: torch.Tensor, q_weight: torch.Tensor, c_weight: torch.Tensor,
                  cos_sin: Optional[torch.Tensor], cq_out: torch.Tensor, view,
                  row_slot: torch.Tensor, row_pos: torch.Tensor, q_rank: int, kv_rank: int,
-                 rot_dim: int, eps: float, write_cache: bool = True) -> None:
+                 rot_dim: int, eps: float, write_cache: bool = True, clear: bool = False) -> None:
     """From proj (float32 [rows, >= q_rank + kv_rank + rot_dim]): the normed query latent into
     ``cq_out`` and the key row [normed latent | rotated key part] into the paged cache ``view``
     (K plane whole, V plane the latent alone).  ``cos_sin``: float32 [rows, pairs, 2]."""
@@ -1113,11 +1114,12 @@ def latent_store(proj: torch.Tensor, q_weight: torch.Tensor, c_weight: torch.Ten
                                   _dt(cq_out), view.page_stride, _ptr(view.block_table),
                                   view.block_table.stride(0), _ptr(row_slot), _ptr(row_pos), rows,
                                   view.page_size, q_rank, kv_rank, rot_dim, float(eps),
-                                  int(write_cache), _stream()), "latent_store")
+                                  int(write_cache), int(clear), _stream()), "latent_store")
 
 
 def latent_query(q: torch.Tensor, cos_sin: Optional[torch.Tensor], q_plain: torch.Tensor,
-                 q_full: torch.Tensor, heads: int, dim: int, rot_dim: int, kv_rank: int) -> None:
+                 q_full: torch.Tensor, heads: int, dim: int, rot_dim: int, kv_rank: int,
+                 clear: bool = False) -> None:
     """From q (float32 [rows, heads * (dim + rot_dim)]): every head's plain part rounded into
     ``q_plain`` [rows, heads * dim], its rotated part into ``q_full`` [rows, heads * (kv_rank +
     rot_dim)] behind the first kv_rank channels."""
@@ -1128,7 +1130,7 @@ def latent_query(q: torch.Tensor, cos_sin: Optional[torch.Tensor], q_plain: torc
     half = 0 if cos_sin is None else cos_sin.shape[1]
     _check(lib().llm_latent_query(_ptr(q), q.stride(0), _ptr(cos_sin), half, _ptr(q_plain),
                                   _ptr(q_full), _dt(q_full), rows, heads, dim, rot_dim, kv_rank,
-                                  _stream()), "latent_query")
+                                  int(clear), _stream()), "latent_query")
 
 
 HEAD_LINEAR_SIMT_ROWS = 128     # up to so many rows the per-head maps are one CUDA-core launch
@@ -1206,7 +1208,7 @@ def moe_gate_up_rows(h: torch.Tensor, gate_up: torch.Tensor, ids: torch.Tensor,
 
 def moe_down_rows(act: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
                   y: torch.Tensor, accumulate: bool, shared: Optional[torch.Tensor] = None,
-                  shared_gate: Optional[torch.Tensor] = None) -> None:
+                  shared_gate: Optional[torch.Tensor] = None, clear_shared: bool = False) -> None:
     """y[r] (+)= sum_k wts[r, k] Wd_e act[r, k] (+ sigmoid(shared_gate[r]) shared[r]);
     down [E, width, ff]; y, shared float32 [rows, width]; shared_gate float32 [rows] (strided)."""
     _cuda(act, down, ids, wts, y, shared, shared_gate)
@@ -1221,7 +1223,7 @@ def moe_down_rows(act: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, wts:
                                    _ptr(shared_gate),
                                    shared_gate.stride(0) if shared_gate is not None else 0,
                                    _ptr(y), _dt(act), rows, width, ff, top, int(accumulate),
-                                   _stream()), "moe_down_rows")
+                                   int(clear_shared), _stream()), "moe_down_rows")
 
 
 def moe_grouped_ok(h_dtype: torch.dtype, width: int, ff: int) -> bool:
@@ -1262,7 +1264,7 @@ def moe_gather(h: torch.Tensor, pos: torch.Tensor, xp: torch.Tensor, top: int) -
 
 def moe_combine(d: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, y: torch.Tensor,
                 accumulate: bool, shared: Optional[torch.Tensor] = None,
-                shared_gate: Optional[torch.Tensor] = None) -> None:
+                shared_gate: Optional[torch.Tensor] = None, clear_shared: bool = False) -> None:
     """y[r] (+)= sum_k wts[r, k] d[pos[r, k]] (+ sigmoid(shared_gate[r]) shared[r])."""
     _cuda(d, pos, wts, y, shared, shared_gate)
     rows, top = wts.shape
@@ -1273,7 +1275,8 @@ def moe_combine(d: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, y: torch.
         assert shared.dtype == torch.float32 and shared.is_contiguous()
     _check(lib().llm_moe_combine(_ptr(d), _ptr(pos), _ptr(wts), _ptr(shared), _ptr(shared_gate),
                                  shared_gate.stride(0) if shared_gate is not None else 0, _ptr(y),
-                                 rows, width, top, int(accumulate), _stream()), "moe_combine")
+                                 rows, width, top, int(accumulate), int(clear_shared), _stream()),
+           "moe_combine")
 
 
 def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,

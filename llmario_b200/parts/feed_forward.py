@@ -107,10 +107,14 @@ class GatedFeedForward:
             self.plain.forward(ctx, h, x, accumulate=accumulate)
             return
         rows = ctx.rows
-        gu = ctx.buffer("ffn.gate_up", (rows, 2 * self.ff), torch.float32)
-        self.gate_up(h, gu)
+        # (few rows: the product adds partial sums into a buffer kept at zero, which the
+        # activation kernel clears again)
+        kept_zero = rows <= kernels.SPLIT_K_MAX_ROWS
+        gu = ctx.buffer("ffn.gate_up.z" if kept_zero else "ffn.gate_up", (rows, 2 * self.ff),
+                        torch.float32, zero=kept_zero)
+        self.gate_up(h, gu, out_is_zero=kept_zero)
         act = ctx.buffer("ffn.act", (rows, self.ff))
-        kernels.gated_act(gu, self.gate_up_bias, act, self.activation)
+        kernels.gated_act(gu, self.gate_up_bias, act, self.activation, clear=kept_zero)
         self.down(act, x, accumulate=accumulate)
 
 
@@ -163,9 +167,13 @@ class RoutedExperts:
             self.router(h, z)
             kernels.moe_route(z, E, top, ids, wts)
         shared = gate = None
+        kept_zero = rows <= kernels.SPLIT_K_MAX_ROWS
         if self.shared is not None:
-            shared = ctx.buffer("moe.shared", (rows, self.hidden), torch.float32)
-            self.shared.forward(ctx, h, shared, accumulate=False)
+            # (few rows: the shared expert adds into a buffer kept at zero, cleared by the kernel
+            # that sums the experts)
+            shared = ctx.buffer("moe.shared.z" if kept_zero else "moe.shared", (rows, self.hidden),
+                                torch.float32, zero=kept_zero)
+            self.shared.forward(ctx, h, shared, accumulate=kept_zero)
             gate = z[:, E]
         if kernels.moe_grouped_ok(h.dtype, self.hidden, self.ff) and self.grouped:
             # sorted by expert into tiles of rows, two grouped tensor-core products, one sum
@@ -181,11 +189,12 @@ class RoutedExperts:
             kernels.gemm_grouped(xp, self.gate_up, act, tile_group, bn, gated=True)
             d = ctx.buffer("moe.down", (tiles * bn, self.hidden), torch.float32)
             kernels.gemm_grouped(act, self.down, d, tile_group, bn, gated=False)
-            kernels.moe_combine(d, pos, wts, x, accumulate, shared, gate)
+            kernels.moe_combine(d, pos, wts, x, accumulate, shared, gate, clear_shared=kept_zero)
             return
         act = ctx.buffer("moe.act", (rows, top, self.ff))
         kernels.moe_gate_up_rows(h, self.gate_up, ids, act)
-        kernels.moe_down_rows(act, self.down, ids, wts, x, accumulate, shared, gate)
+        kernels.moe_down_rows(act, self.down, ids, wts, x, accumulate, shared, gate,
+                              clear_shared=kept_zero)
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

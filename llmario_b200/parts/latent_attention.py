@@ -85,17 +85,24 @@ class LatentAttention:
         view = ctx.cache.view(call.cache_entry)
         if view is None:
             raise RuntimeError(f"run-order entry {call.index}: attention needs a cache")
-        proj = ctx.buffer("latent.proj", (rows, self.down_proj.out_features), torch.float32)
-        self.down_proj(h, proj)
+        # With few rows the products are cut along K and add partial sums: their destinations are
+        # then buffers that are created as zeros and that the kernels which consume them clear
+        # again, so no clearing launch runs.
+        kept_zero = rows <= kernels.SPLIT_K_MAX_ROWS
+        z = ".z" if kept_zero else ""
+        proj = ctx.buffer("latent.proj" + z, (rows, self.down_proj.out_features), torch.float32,
+                          zero=kept_zero)
+        self.down_proj(h, proj, out_is_zero=kept_zero)
         angles = self.position.step_angles(ctx) if self.position is not None else None
         cq = ctx.buffer("latent.cq", (rows, self.q_rank))
         kernels.latent_store(proj, self.q_gain, self.c_gain, angles, cq, view, ctx.row_slot,
-                             ctx.row_pos, self.q_rank, C, R, self.eps, call.writes_cache)
-        q = ctx.buffer("latent.q", (rows, H * (D + R)), torch.float32)
-        self.q_proj(cq, q)
+                             ctx.row_pos, self.q_rank, C, R, self.eps, call.writes_cache,
+                             clear=kept_zero)
+        q = ctx.buffer("latent.q" + z, (rows, H * (D + R)), torch.float32, zero=kept_zero)
+        self.q_proj(cq, q, out_is_zero=kept_zero)
         q_plain = ctx.buffer("latent.q_plain", (rows, H * D))
         q_full = ctx.buffer("latent.q_full", (rows, H * self.key_dim))
-        kernels.latent_query(q, angles, q_plain, q_full, H, D, R, C)
+        kernels.latent_query(q, angles, q_plain, q_full, H, D, R, C, clear=kept_zero)
         kernels.head_linear(q_plain.view(rows, H, D), self.key_maps,
                             q_full.view(rows, H, self.key_dim)[:, :, :C])
         # sum_j p_j c_j per head.  The tensor-core kernels work on whole value rows (what lies
