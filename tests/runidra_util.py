@@ -62,6 +62,9 @@ CONFIGS: Dict[str, dict] = {
     "latent": config([latent(mlp=dense(80))]),
     "latent_tc": config([latent(heads=4, dim=32, rot_dim=32, vdim=32, q_rank=64, kv_rank=96,
                                 window=40)], width=128),
+    # sixteen heads on the one key row of 64 channels: in 16 bits the sixteen-row decode kernel
+    "latent_h16": config([latent(heads=16, dim=16, rot_dim=32, vdim=8, q_rank=32, kv_rank=32,
+                                 window=24, mlp=dense(64))], streams=2),
     "latent_whole": config([latent(heads=2, dim=24, rot_dim=8, vdim=16, window=None, scale=0.2,
                                    dims=4)], streams=None),
     "latent_odd": config([latent(heads=5, dim=6, rot_dim=10, vdim=7, q_rank=9, kv_rank=13,

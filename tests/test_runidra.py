@@ -374,7 +374,7 @@ def test_portions_of_many_sizes(name, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ("mix", "loop_all", "latent_tc", "odd", "experts_tc"))
+@pytest.mark.parametrize("name", ("mix", "loop_all", "latent_tc", "latent_h16", "odd", "experts_tc"))
 def test_mixed_batches_and_reused_slots(name, dtype):
     """Four request slots, six requests of unequal lengths: portions of some beside single tokens
     of others, requests that pause, requests that end and whose slot and pages the next one
