@@ -139,8 +139,8 @@ def kernel_table(width: int = 4096, tokens: int = 2048, batch: int = 64, heads: 
         us = _time(lambda: kernels.memory_out_norm(o, gates[:, 2 * H:], proj[:, 2 * H * K + H * V:ci], wv, gated,
                                                    H, V, 1e-6, 1e-6), flush=flush)
         rec(f"memory_out_norm ({label})", us, rows * H * V * (4 + 4 + 2))
-        # ---- attention through latents: key rows of 96 + 32 channels, one key head
-        C, R, D, Vd, Rq = 96, 32, 96, 128, max(64, width // 4)
+        # ---- attention through latents: key rows of 64 + 64 channels, one key head
+        C, R, D, Vd, Rq = 64, 64, 64, 128, max(64, width // 4)
         hd = C + R
         page, n_pages = 64, -(-(window + tokens) // 64) + 1
         ctx_len = window if single else 0

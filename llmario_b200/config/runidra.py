@@ -6,8 +6,7 @@ low-rank latents, with one rotated key part for all heads, a sliding window and 
 softmax) and an optional feed-forward (``dense``: gated, tanh-form gelu, biases; ``moe``: routed
 experts with a gated shared expert).  Sublayers are pre-norm.  With the key ``streams`` the residual is kept as that many streams
 that every sublayer reads through learned weights and writes through a learned mixing matrix.
-``loop`` runs a range of layers several times in a row with the same weights, each pass with a
-cache of its own.  The logits are scaled and soft-capped.  Every size and constant that can differ
+``loop`` repeats a range of layers (shared weights, a cache or state per repetition).  The logits are scaled and soft-capped.  Every size and constant that can differ
 between two models of the design is read here and nowhere else; tensor names follow ``l<i>.<part>``.
 """
 from __future__ import annotations
@@ -275,14 +274,14 @@ def sized_like(width: int, ff: int, heads: int, head_dim: int, layers: int, voca
     """A configuration for models with random weights at the sizes of a transformer: layers
     repeating (latent attention + dense, matrix memory + routed experts, latent attention +
     dense, latent attention + routed experts) on two residual streams.  The attention keeps a
-    latent of 96 and a rotated part of 32 per token (one key row of 128; smaller for heads below
+    latent of 64 and a rotated part of 64 per token (one key row of 128; smaller for heads below
     64), queries through a latent of a quarter of the width; the memory has heads of 128 x 128
     (at most half the width); at most 16 attention heads; the routed experts are
     `experts` of width ff / top with `top` chosen, beside a shared one of the same width."""
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top},
            "shared": {"ff": ff // top}}
-    rot = min(32, head_dim // 2)
+    rot = min(64, head_dim // 2)
     heads = min(heads, 16)      # the tensor-core decode kernels take up to 16 query heads per key head
     att = {"heads": heads, "dim": head_dim - rot, "rot_dim": rot, "vdim": head_dim,
            "q_rank": max(64, width // 4), "kv_rank": 128 - rot if head_dim >= 64 else 2 * head_dim,

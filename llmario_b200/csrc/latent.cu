@@ -1,6 +1,6 @@
 // Attention through low-rank latents.  A token's keys and values of all heads are functions of
 // one latent vector c (kv_rank numbers) and one rotated key part shared by the heads (rot_dim
-// numbers); only those are cached, as one key row [c | rotated part] of kv_rank + rot_dim
+// numbers); the cache holds just these, as one key row [c | rotated part] of kv_rank + rot_dim
 // channels.  The heads' key and value maps are folded to the query's and the output's side:
 //   score_h = (U_k,h^T q_h) . c + q_rot,h . k_rot          out_h = U_v,h (sum_j p_j c_j)
 // so attention runs as one shared key head whose values are the first kv_rank channels of its keys.

@@ -21,7 +21,7 @@ namespace {
 constexpr int MAX_TOP = 16;
 
 // One warp per row.  The k-th choice is the largest logit not chosen before (the lowest index
-// among equals); weights are the softmax over the chosen logits only.
+// among equals); the weights are a softmax in which only the chosen logits take part.
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, int z_stride, int rows, int E,
                                                         int top, int* __restrict__ ids, float* __restrict__ wts) {
   pdl_trigger();

@@ -356,7 +356,7 @@ class ModelRunner:
             x = ctx.buffer("x", (ctx.rows, m.hidden_size), torch.float32)
             m.embedding.forward(ctx, ctx.tokens, x)
         else:
-            # several residual streams, all equal to the embedding output at the start
+            # several residual streams: each begins as a copy of what the embedding gives
             x = ctx.buffer("x", (streams, ctx.rows, m.hidden_size), torch.float32)
             m.embedding.forward(ctx, ctx.tokens, x[0])
             kernels.stream_fill(x)

@@ -5,8 +5,8 @@ crates/engine/cpu/src/ops.rs:83-99).  Gate and up are one product over stacked r
 Beside it: the same form with a choice of activation and optional biases (kind ``gated``), and
 routed experts (kind ``moe``): a router's logits (32-bit) choose ``top`` of ``experts`` small
 silu-gated feed-forwards per token, whose outputs are summed with the softmax over the chosen
-logits as weights; an optional shared feed-forward runs for every token and is added multiplied
-by the sigmoid of one more projection of the input (one number per token)."""
+logits as weights; an optional shared feed-forward is applied to all tokens and added with a
+per-token scalar weight, the sigmoid of one more projection of the input."""
 from __future__ import annotations
 
 from typing import Dict

@@ -2,19 +2,19 @@
 
 With ``h`` the mixer's input, per token:
 
-* ``c_q = norm(W_dq h)`` (gain ``dq_norm``), ``q = W_uq c_q``, laid out head by head as
+* ``c_q = norm(W_dq h)`` (gain ``dq_norm``), ``q = W_uq c_q``; every head's slice of q is
   [``head_dim`` plain | ``rot_dim`` rotated];
 * ``W_dkv h`` = [``kv_rank`` numbers, normed with gain ``dkv_norm``: the latent ``c`` | ``rot_dim``
   numbers, not normed: one rotated key part shared by all heads];
 * head h's plain key is ``U_k,h c`` and its value ``U_v,h c``; the score of a query and a key is
   ``(q_plain . k_plain + q_rot . k_rot) * scale``;
 * the rotation turns adjacent pairs (2i, 2i + 1) of the rotated parts by ``pos * base^(-2i/dims)``;
-* a query sees itself and the ``window - 1`` tokens before it; an optional ``sink`` per head adds
+* a query at position p sees the keys at p - window + 1 .. p; an optional ``sink`` per head adds
   ``exp(sink)`` to the softmax's sum (a key without a value);
 * the heads' outputs, concatenated, are projected by ``W_o``.
 
-Only ``c`` and the rotated key part are cached: one key row of ``kv_rank + rot_dim`` channels per
-token.  The heads' key maps are applied to the queries (``U_k,h^T q_plain``) and their value maps
+The cache holds ``c`` and the rotated key part, nothing per head: one key row of ``kv_rank +
+rot_dim`` channels per token.  The heads' key maps are applied to the queries (``U_k,h^T q_plain``) and their value maps
 to the attention's output (``U_v,h sum_j p_j c_j``), so the attention itself runs as one shared key
 head whose values are the first ``kv_rank`` channels of its keys.
 """

@@ -60,7 +60,7 @@ CONFIGS: Dict[str, dict] = {
     "memory_wide": config([mlstm(heads=1, dim=72, vdim=16, cap=6.0)], width=48, streams=1),
     "memory_big_key": config([mlstm(heads=3, dim=136, vdim=20)], streams=3),
     "latent": config([latent(mlp=dense(80))]),
-    "latent_tc": config([latent(heads=4, dim=32, rot_dim=32, vdim=32, q_rank=64, kv_rank=96,
+    "latent_tc": config([latent(heads=4, dim=48, rot_dim=16, vdim=32, q_rank=64, kv_rank=112,
                                 window=40)], width=128),
     # sixteen heads on the one key row of 64 channels: in 16 bits the sixteen-row decode kernel
     "latent_h16": config([latent(heads=16, dim=16, rot_dim=32, vdim=8, q_rank=32, kv_rank=32,
